@@ -1,0 +1,188 @@
+/* C ABI of the B200 paged split-KV flash-decoding engine (libpd_b200.so).
+ *
+ * This is the drop-in boundary for the decode hot path of emaanh/paged-attention.
+ * The reference exposes that path only as C++ (namespace decode::); every entry
+ * point here names the C++ declaration it stands in for, by the file's path in
+ * the reference project.  Plain pointers and sizes only; all device pointers are
+ * CUDA device pointers of the current device; `stream` is a cudaStream_t passed
+ * as void* (NULL = default stream).
+ *
+ * Error model: every function that can fail returns a pd_status.  Nothing here
+ * aborts the process, throws across the boundary or traps on the device.  The
+ * message of the calling thread's last failure is pd_last_error().  The C++
+ * wrappers (paged_attention_b200/include) turn PD_INVALID_ARGUMENT into
+ * std::invalid_argument and PD_LENGTH_ERROR into std::length_error, as the
+ * reference throws them.
+ *
+ * Threading: as in the reference, one host thread drives one cache / plan at a
+ * time; objects carry no locks.  One-time kernel configuration is thread-safe.
+ */
+#ifndef PD_B200_H
+#define PD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pd_status {
+    PD_OK               = 0,
+    PD_INVALID_ARGUMENT = 1,  /* std::invalid_argument in the reference */
+    PD_LENGTH_ERROR     = 2,  /* std::length_error in the reference */
+    PD_CUDA_ERROR       = 3,  /* the reference prints and abort()s (include/cuda_check.hpp:9-17) */
+    PD_OUT_OF_PAGES     = 4,  /* append returned false in the reference */
+    PD_KERNEL_TIMEOUT   = 5,  /* a bounded device-side wait expired; see pd_kernel_status */
+    PD_INTERNAL         = 6
+} pd_status;
+
+/* decode::KVDtype (src/decode/decode_types.hpp:8) */
+typedef enum pd_kv_dtype { PD_FP16 = 0, PD_FP8_E4M3 = 1 } pd_kv_dtype;
+
+/* decode::DecodeParams (src/decode/decode_types.hpp:14-45), field for field and
+ * in the same order, so a decode::DecodeParams can be passed as a pd_params. */
+typedef struct pd_params {
+    const void* q;              /* half [batch][num_q_heads][head_dim] */
+    void*       out;            /* half [batch][num_q_heads][head_dim] */
+    const void* k_cache;        /* [num_pages][num_kv_heads][page_size][head_dim], fp16 or e4m3 */
+    const void* v_cache;
+    const int*  block_table;    /* [num_slots][block_table_stride] physical page ids */
+    const int*  seq_lens;       /* [num_slots] */
+    const int*  slot_ids;       /* [batch] cache slot per batch row; NULL = identity */
+    int         block_table_stride;
+    int         batch;
+    int         num_q_heads;
+    int         num_kv_heads;
+    int         head_dim;
+    int         page_size;
+    float       sm_scale;
+    float       k_scale;
+    float       v_scale;
+    const void* segments;       /* int4 (row, kv head, token begin, token end) per segment */
+    const int*  cta_seg_begin;  /* [num_ctas + 1] */
+    const int*  item_seg_begin; /* [batch * num_kv_heads + 1] */
+    int         num_ctas;
+    int         needs_merge;
+    float*      partial_out;    /* [num_segments][group][head_dim] */
+    float*      partial_lse;    /* [num_segments][group] */
+} pd_params;
+
+/* PagedKVCache::Config (src/decode/paged_kv_cache.hpp:19-29) */
+typedef struct pd_cache_config {
+    int   num_pages;
+    int   page_size;
+    int   num_kv_heads;
+    int   head_dim;
+    int   max_slots;
+    int   max_pages_per_slot;
+    int   dtype;      /* pd_kv_dtype */
+    float k_scale;    /* stored = value / scale (FP8 only) */
+    float v_scale;
+} pd_cache_config;
+
+typedef struct pd_plan        pd_plan;         /* decode::DecodePlan  (src/decode/decode.hpp:21-27) */
+typedef struct pd_device_plan pd_device_plan;  /* decode::DevicePlan  (src/decode/decode.hpp:44-62) */
+typedef struct pd_cache       pd_cache;        /* decode::PagedKVCache (src/decode/paged_kv_cache.hpp:17-93) */
+
+/* Message of this thread's most recent failure ("" if none). */
+const char* pd_last_error(void);
+/* Library version string. */
+const char* pd_version(void);
+
+/* kv_dtype_bytes / kv_dtype_name (src/decode/decode_types.hpp:10-11) */
+int         pd_kv_dtype_bytes(int dtype);
+const char* pd_kv_dtype_name(int dtype);
+
+/* decode::tile_tokens / wave_ctas / default_ctas (src/decode/decode.hpp:30-35).
+ * tile_tokens needs no GPU; the other two query the current device. */
+int pd_tile_tokens(int dtype, int head_dim, int group, int* out);
+int pd_wave_ctas(int dtype, int head_dim, int group, int* out);
+int pd_default_ctas(int dtype, int head_dim, int group, int* out);
+
+/* Tuning knob with no counterpart in the reference, whose launch shape is a
+ * compile-time constant (src/decode/decode.cu:14): selects one of the compiled CTA
+ * shapes / pipeline depths (0 = default).  Also read once from the environment
+ * variable PD_B200_VARIANT.  Changes pd_tile_tokens, so re-plan afterwards. */
+int pd_set_kernel_variant(int variant);
+int pd_kernel_variant(void);
+
+/* decode::make_plan (src/decode/decode.hpp:38-39).  num_ctas <= 0 uses
+ * pd_default_ctas (needs a GPU).  The plan is a host object; free it with
+ * pd_plan_free.  PD_INVALID_ARGUMENT if num_q_heads is not a multiple of
+ * num_kv_heads or a sequence length is <= 0. */
+int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                 int head_dim, int num_ctas, pd_plan** out);
+/* The same cut with an explicit tile size (tokens per work unit) instead of the
+ * kernel's own; pure host arithmetic.  Used to check the planner against the
+ * reference's published (ctas, segments) pairs, which were made at tile 64. */
+int pd_make_plan_tiled(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                       int num_ctas, pd_plan** out);
+void       pd_plan_free(pd_plan* plan);
+int        pd_plan_num_ctas(const pd_plan* plan);
+int        pd_plan_tile(const pd_plan* plan);
+int        pd_plan_num_segments(const pd_plan* plan);
+int        pd_plan_num_items(const pd_plan* plan);
+const int* pd_plan_segments(const pd_plan* plan);        /* 4 ints per segment */
+const int* pd_plan_cta_seg_begin(const pd_plan* plan);   /* num_ctas + 1 */
+const int* pd_plan_item_seg_begin(const pd_plan* plan);  /* num_items + 1 */
+
+/* decode::DevicePlan (src/decode/decode.hpp:44-62): device copy of a plan plus the
+ * partial-result workspace, grow-only. */
+int  pd_device_plan_create(pd_device_plan** out);
+void pd_device_plan_destroy(pd_device_plan* dp);
+int  pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, int head_dim, void* stream);
+int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
+
+/* decode::paged_decode (src/decode/decode.hpp:66): the split kernel and, if any
+ * (row, head) was split across CTAs, the merge.  head_dim 128; group 1, 2, 4, 8.
+ * num_pages > 0 bounds the page coordinate of the TMA descriptors (page ids
+ * outside [0, num_pages) then read as zeros instead of touching memory);
+ * pd_paged_decode passes "unknown". */
+int pd_paged_decode(int dtype, const pd_params* p, void* stream);
+int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream);
+
+/* Device status word of the last decode launched by this thread's library state:
+ * 0 = every bounded wait completed.  Reads it back (synchronises `stream`).
+ * Nonzero encodes (code << 24 | cta) of the first wait that gave up. */
+int pd_kernel_status(void* stream, unsigned* status);
+
+/* append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers:
+ * scatter n tokens of fp16 K/V ([n][num_kv_heads][head_dim], device) into the
+ * pools through one slot's block-table row (device), quantising to E4M3 with
+ * value * (1/scale) when dtype is FP8. */
+int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
+                     const int* d_block_table_row, int start_pos, int n, int num_kv_heads,
+                     int head_dim, int page_size, float k_scale, float v_scale, void* stream);
+
+/* decode::PagedKVCache (src/decode/paged_kv_cache.hpp:31-73). */
+size_t pd_cache_bytes_per_page(const pd_cache_config* cfg);
+int    pd_cache_pages_for_budget(const pd_cache_config* cfg, size_t budget_bytes);
+int    pd_cache_create(const pd_cache_config* cfg, pd_cache** out);
+void   pd_cache_destroy(pd_cache* c);
+int    pd_cache_admit(pd_cache* c);   /* slot, or -1 when every slot is in use */
+/* PD_OK, PD_OUT_OF_PAGES (nothing changed), PD_INVALID_ARGUMENT, PD_LENGTH_ERROR */
+int    pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, int n, void* stream);
+int    pd_cache_release(pd_cache* c, int slot);
+void   pd_cache_shuffle_free_pages(pd_cache* c, unsigned seed);
+int    pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads, int num_ctas, void* stream);
+int    pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream);
+int    pd_cache_decode(pd_cache* c, const void* d_q, void* d_out, int batch, int num_q_heads,
+                       int num_ctas, void* stream);
+const pd_plan* pd_cache_last_plan(const pd_cache* c);  /* borrowed; valid until the next plan */
+int    pd_cache_params(const pd_cache* c, pd_params* out);
+int    pd_cache_seq_len(const pd_cache* c, int slot);
+int    pd_cache_occupied(const pd_cache* c, int slot);
+int    pd_cache_free_pages(const pd_cache* c);
+int    pd_cache_max_seq_len(const pd_cache* c);
+size_t pd_cache_total_bytes(const pd_cache* c);
+int    pd_cache_config_of(const pd_cache* c, pd_cache_config* out);
+/* Host copy of a slot's page ids; returns the count and writes up to cap of them. */
+int    pd_cache_block_table(const pd_cache* c, int slot, int* out, int cap);
+/* Free list, back = next page handed out; returns the count. */
+int    pd_cache_free_list(const pd_cache* c, int* out, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PD_B200_H */

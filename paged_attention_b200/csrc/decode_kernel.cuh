@@ -1,0 +1,608 @@
+#pragma once
+// Paged split-KV flash-decoding for sm_100a: TMA + mbarrier pipeline, warp-specialised.
+//
+// Stands in for paged_decode_kernel / merge_segments_kernel of the reference
+// (src/decode/decode_kernels.cuh:123-403, 409-432) and keeps their contract: a
+// persistent grid of num_ctas CTAs, CTA c streams segments
+// [cta_seg_begin[c], cta_seg_begin[c+1]) of the host-built plan; a (row, kv head)
+// covered by one segment is written to `out` directly, otherwise each segment
+// leaves a normalised fp32 partial + base-2 LSE for the merge kernel.
+//
+// What is different from the reference, and why:
+//  * K/V pages are brought in by TMA (cp.async.bulk.tensor) from one tensor map
+//    over the whole pool [page][kv head][token][dim]; the block-table entry is the
+//    page coordinate.  One producer warp issues the copies (each lane owns one box
+//    and prefetches its page ids a chunk ahead), WARPS consumer warps do the math.
+//    The two sides meet only through full/empty mbarriers, so loads run ahead of
+//    the math across tile and segment boundaries by STAGES-1 tiles.
+//  * Tokens are the M dimension of mma.m16n8k16 and the (<= 8) query heads of the
+//    GQA group the N dimension: S^T = K Q^T and O^T = V^T P^T.  No MMA row is
+//    padding, which halves the tensor instruction count of the reference's
+//    heads-as-M layout.  P^T reaches its B-fragment layout with two movmatrix.
+//  * Shared memory uses the TMA 128-byte swizzle; fp16 rows are split in two
+//    64-element panels so a box lands as [panel][token][128 B].  ldmatrix
+//    (fp16) and 16-byte loads (fp8) are conflict-free for page sizes >= 8.
+//  * Every wait is bounded; on expiry the CTA records a code in a status word,
+//    raises a CTA-wide abort flag and drains its copies.  Nothing traps.
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "pd_b200.h"
+
+namespace pdk {
+
+constexpr int HEAD_DIM = 128;
+constexpr int OSTRIDE  = HEAD_DIM + 4;   // padded row of the cross-warp merge scratch (floats)
+
+// status word codes (code << 24 | blockIdx)
+constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a tile
+constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
+constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
+constexpr unsigned ST_SYNC_TIMEOUT  = 4;   // a consumer warp gave up waiting for its siblings
+
+template<int WARPS_, int GROUPS_PER_WARP_, int STAGES_, int MIN_CTAS_>
+struct Config {
+    static constexpr int WARPS           = WARPS_;             // consumer warps (one more warp produces)
+    static constexpr int GROUPS_PER_WARP = GROUPS_PER_WARP_;   // 16-token groups per warp per tile
+    static constexpr int STAGES          = STAGES_;
+    static constexpr int MIN_CTAS        = MIN_CTAS_;
+};
+
+template<typename KV, int GROUP, typename C>
+struct Shape {
+    static constexpr int THREADS     = (C::WARPS + 1) * 32;
+    static constexpr int CONSUMERS   = C::WARPS * 32;
+    static constexpr int TILE        = C::WARPS * C::GROUPS_PER_WARP * 16;
+    static constexpr int ROW_BYTES   = HEAD_DIM * static_cast<int>(sizeof(KV));
+    static constexpr int TILE_BYTES  = TILE * ROW_BYTES;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int PIPE_BYTES  = C::STAGES * STAGE_BYTES;
+    // The cross-warp merge runs over at most 4 heads at a time (two passes for a
+    // group of 8), which keeps two CTAs of the fp16 configuration on one SM.
+    static constexpr int GROUP_PAD   = GROUP < 2 ? 2 : (GROUP > 4 ? 4 : GROUP);
+    static constexpr int PASSES      = GROUP > 4 ? 2 : 1;
+    static constexpr int MERGE_BYTES = (C::WARPS * GROUP_PAD * OSTRIDE + 2 * C::WARPS * 8) * 4;
+    static constexpr int BAR_BYTES   = 2 * C::STAGES * 8 + 16;
+    // +1024: the pipeline is aligned to the 128B-swizzle period by hand
+    static constexpr int SMEM_BYTES  = 1024 + PIPE_BYTES + MERGE_BYTES + BAR_BYTES;
+    static_assert(GROUP >= 1 && GROUP <= 8, "a KV group fills the 8 columns of one MMA");
+};
+
+// ---- PTX wrappers -------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about 2^31 SM cycles (~1 s).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 31)) return false;
+    }
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// One box of a 4-D (fp8) or 5-D (fp16) tensor map into shared memory.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128_zero(uint32_t addr) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" :: "r"(addr), "r"(0u) : "memory");
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+// D(16x8) += A(16x16, row) * B(16x8, col), fp16 in, fp32 accumulate.
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t fp8x2_to_half2(uint32_t two_bytes) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Byte offset, inside one K or V tile, of the 128-byte shared-memory row that
+// holds token `t` (0..TILE-1), panel `h` (fp16: dims 64h..64h+63; fp8: h = 0).
+// A tile is a run of boxes of 2^btl tokens; a box is [panel][token][128 B].
+template<typename KV>
+__device__ __forceinline__ uint32_t row_offset(int t, int h, int btl) {
+    constexpr int PANELS = sizeof(KV);   // 2 for fp16, 1 for fp8
+    const int box = t >> btl, r = t & ((1 << btl) - 1);
+    return static_cast<uint32_t>(((box * PANELS + h) << btl) + r) << 7;
+}
+// Address of 16-byte chunk c of a 128-byte row under the TMA 128B swizzle
+// (chunk index XOR row index mod 8; the tile base is 1024-byte aligned).
+__device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
+    return row_off + (((c ^ (row_off >> 7)) & 7) << 4);
+}
+
+// ---- decode kernel ---------------------------------------------------------------
+
+template<typename KV, int GROUP, typename C>
+__global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
+paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const int btl /* log2(box tokens) */,
+                    unsigned* __restrict__ status)
+{
+    using S = Shape<KV, GROUP, C>;
+    constexpr bool FP8 = sizeof(KV) == 1;
+    constexpr int STAGES = C::STAGES;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t pipe = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* gen = smem_raw + (pipe - smem_u32(smem_raw));   // generic view of the aligned base
+    float* w_o = reinterpret_cast<float*>(gen + S::PIPE_BYTES);
+    float* w_m = w_o + C::WARPS * S::GROUP_PAD * OSTRIDE;
+    float* w_l = w_m + C::WARPS * 8;
+    const uint32_t bars = pipe + S::PIPE_BYTES + S::MERGE_BYTES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + S::PIPE_BYTES + S::MERGE_BYTES + 2 * STAGES * 8 + 8);
+    auto full_bar  = [&](int s) { return bars + s * 8; };
+    auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
+    const uint32_t sync_bar = bars + 2 * STAGES * 8;   // consumer-warp rendezvous (bounded, unlike bar.sync)
+
+    const int seg_begin = p.cta_seg_begin[blockIdx.x];
+    const int seg_end   = p.cta_seg_begin[blockIdx.x + 1];
+    if (seg_begin >= seg_end) return;
+
+    const int tid  = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), C::WARPS); }
+        mbar_init(sync_bar, C::WARPS);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int4* segments = static_cast<const int4*>(p.segments);
+    auto fail = [&](unsigned code) {
+        atomicCAS(status, 0u, (code << 24) | (blockIdx.x & 0xffffffu));
+        *abort_flag = 1;
+    };
+
+    if (warp == C::WARPS) {
+        // ================= producer warp =================
+        const int bt_tokens = 1 << btl;                 // tokens per box
+        const int bpt       = S::TILE >> btl;           // boxes per tile
+        const uint32_t box_bytes = static_cast<uint32_t>(bt_tokens) * S::ROW_BYTES;
+        const uint64_t pol = l2_evict_first_policy();
+        const int ps = p.page_size;
+        int issued = 0;                                 // tiles issued so far (stage = issued % STAGES)
+        bool ok = true;
+
+        auto table_of = [&](int b) {
+            const int slot = p.slot_ids ? __ldg(p.slot_ids + b) : b;
+            return p.block_table + static_cast<size_t>(slot) * p.block_table_stride;
+        };
+        // Issue the copies of one tile: lanes [lane0, lane0 + nb) own one box each when
+        // the tile has <= 32 boxes, otherwise every lane walks boxes lane, lane+32, ...
+        auto issue_tile = [&](const int4& sg, int tile_tok, int my_page, int lane0, const int* bt) -> bool {
+            const int stage = issued % STAGES;
+            const uint32_t par = ((issued / STAGES) & 1) ^ 1;
+            if (!mbar_wait(empty_bar(stage), par)) { if (lane == 0) fail(ST_EMPTY_TIMEOUT); return false; }
+            if (*abort_flag) return false;
+            const int valid = min(S::TILE, sg.w - tile_tok);
+            const int nb = (valid + bt_tokens - 1) >> btl;
+            if (lane == 0) mbar_expect_tx(full_bar(stage), 2u * nb * box_bytes);
+            __syncwarp();
+            const uint32_t k_dst = pipe + stage * S::STAGE_BYTES;
+            const uint32_t v_dst = k_dst + S::TILE_BYTES;
+            auto copy_box = [&](int j, int page) {
+                const int tok_in_page = (tile_tok + (j << btl)) % ps;
+                if constexpr (FP8) {
+                    tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
+                    tma_load_4d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
+                } else {
+                    tma_load_5d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page, pol);
+                    tma_load_5d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page, pol);
+                }
+            };
+            if (bpt <= 32) {
+                const int j = lane - lane0;
+                if (j >= 0 && j < nb) copy_box(j, my_page);
+            } else {
+                for (int j = lane; j < nb; j += 32)
+                    copy_box(j, __ldg(bt + (tile_tok + (j << btl)) / ps));
+            }
+            issued++;
+            return true;
+        };
+
+        // A chunk is up to 32 boxes of one segment: lane l owns box l of the chunk.
+        const int chunk_tiles  = bpt <= 32 ? 32 / bpt : 1;
+        const int chunk_tokens = chunk_tiles * S::TILE;
+        int  seg = seg_begin;
+        int4 sg  = __ldg(segments + seg);
+        const int* bt = table_of(sg.x);
+        int  tok = sg.z;
+        auto page_of = [&](const int4& s, const int* table, int chunk_tok) {
+            const int t = chunk_tok + (lane << btl);
+            return (bpt <= 32 && t < s.w) ? __ldg(table + t / ps) : 0;
+        };
+        int page = page_of(sg, bt, tok);
+        while (ok && seg < seg_end) {
+            // Look one chunk ahead (possibly into the next segment) so its page ids are
+            // in flight while this chunk's copies are issued.
+            int  n_seg = seg, n_tok = tok + chunk_tokens;
+            int4 n_sg = sg;
+            const int* n_bt = bt;
+            if (n_tok >= sg.w) {
+                n_seg = seg + 1;
+                if (n_seg < seg_end) { n_sg = __ldg(segments + n_seg); n_bt = table_of(n_sg.x); n_tok = n_sg.z; }
+            }
+            const int n_page = n_seg < seg_end ? page_of(n_sg, n_bt, n_tok) : 0;
+            for (int ti = 0; ti < chunk_tiles; ti++) {
+                const int tile_tok = tok + ti * S::TILE;
+                if (tile_tok >= sg.w) break;
+                if (!issue_tile(sg, tile_tok, page, ti * bpt, bt)) { ok = false; break; }
+            }
+            seg = n_seg; sg = n_sg; bt = n_bt; tok = n_tok; page = n_page;
+        }
+        if (!ok || *abort_flag) {
+            // Drain: no copy may still be in flight towards this CTA's shared memory at exit.
+            for (int i = max(0, issued - STAGES); i < issued; i++)
+                if (!mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1)) { if (lane == 0) fail(ST_DRAIN_TIMEOUT); break; }
+        }
+        return;
+    }
+
+    // ================= consumer warps =================
+    const int g  = lane >> 2;   // fragment row
+    const int qd = lane & 3;    // fragment column pair: this lane owns heads 2qd, 2qd+1
+    const float qk_scale = p.sm_scale * p.k_scale * 1.4426950408889634f;   // softmax runs in base 2
+
+    float acc[8][4];
+    float m_run[2], l_run[2];
+    uint32_t qb[8][2];          // Q^T B-fragments for the 8 k-steps
+
+    int consumed = 0;
+    bool alive = true;
+    uint32_t sync_phase = 0;
+    // All consumer warps meet here; gives up (and aborts the CTA) instead of hanging
+    // if a warp that bailed out never arrives.
+    auto consumer_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sync_bar);
+        const bool ok = mbar_wait(sync_bar, sync_phase);
+        sync_phase ^= 1;
+        if (!ok) { if (lane == 0) fail(ST_SYNC_TIMEOUT); alive = false; }
+        return ok;
+    };
+
+    for (int seg = seg_begin; alive && seg < seg_end; seg++) {
+        const int4 sg = __ldg(segments + seg);
+        // ---- Q fragments: column n = g is query head g of the group (zero when g >= GROUP).
+        {
+            const bool live = g < GROUP;
+            const __half* qrow = static_cast<const __half*>(p.q)
+                + (static_cast<size_t>(sg.x) * p.num_q_heads + sg.y * GROUP + (live ? g : 0)) * HEAD_DIM;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                if constexpr (FP8) {
+                    // k-slots {2qd,2qd+1,2qd+8,2qd+9} of k-step ks are dims db..db+3 (one fp8 word of K)
+                    const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
+                    const uint2 v = *reinterpret_cast<const uint2*>(qrow + db);
+                    qb[ks][0] = live ? v.x : 0u;
+                    qb[ks][1] = live ? v.y : 0u;
+                } else {
+                    const uint32_t lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd);
+                    const uint32_t hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd);
+                    qb[ks][0] = live ? lo : 0u;
+                    qb[ks][1] = live ? hi : 0u;
+                }
+            }
+        }
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+        m_run[0] = m_run[1] = -INFINITY;
+        l_run[0] = l_run[1] = 0.f;
+
+        for (int tok = sg.z; tok < sg.w; tok += S::TILE) {
+            const int stage = consumed % STAGES;
+            if (!mbar_wait(full_bar(stage), (consumed / STAGES) & 1)) { if (lane == 0) fail(ST_FULL_TIMEOUT); alive = false; break; }
+            if (*abort_flag) { alive = false; break; }
+            const uint32_t k_tile = pipe + stage * S::STAGE_BYTES;
+            const uint32_t v_tile = k_tile + S::TILE_BYTES;
+            const int valid = sg.w - tok;   // tokens of this tile that exist (may exceed TILE)
+            bool wrote = false;
+
+#pragma unroll
+            for (int gi = 0; gi < C::GROUPS_PER_WARP; gi++) {
+                const int grp_row = (warp * C::GROUPS_PER_WARP + gi) * 16;
+                if (grp_row >= valid) break;                      // warp-uniform
+                const int grp_valid = valid - grp_row;            // >= 1; < 16 only in a sequence's last group
+
+                if (grp_valid < 16) {
+                    // Rows past the end hold whatever the page or the stage held before; a NaN
+                    // there would survive P = 0 in the PV product, so clear V's dead rows.
+                    constexpr int CH = S::ROW_BYTES / 16;
+                    for (int idx = lane; idx < 16 * CH; idx += 32) {
+                        const int r = idx / CH, c = idx % CH;
+                        if (r >= grp_valid)
+                            sts128_zero(v_tile + row_offset<KV>(grp_row + r, FP8 ? 0 : (c >> 3), btl) + ((c & 7) << 4));
+                    }
+                    wrote = true;
+                    __syncwarp();
+                }
+
+                // ---- 1. S^T = K Q^T : 16 tokens x 8 heads, two interleaved accumulators.
+                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+                if constexpr (!FP8) {
+                    const int t = grp_row + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const uint32_t r0 = row_offset<KV>(t, 0, btl), r1 = row_offset<KV>(t, 1, btl);
+                    const int hi = lane >> 4;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        uint32_t a[4];
+                        ldmatrix_x4(a, k_tile + swz(ks < 4 ? r0 : r1, (ks & 3) * 2 + hi));
+                        if (ks & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
+                        else        mma_16816(s0, a, qb[ks][0], qb[ks][1]);
+                    }
+                } else {
+                    const uint32_t r0 = row_offset<KV>(grp_row + g, 0, btl), r1 = row_offset<KV>(grp_row + g + 8, 0, btl);
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const uint4 lo = lds128(k_tile + swz(r0, 2 * qd + j));
+                        const uint4 hi = lds128(k_tile + swz(r1, 2 * qd + j));
+                        const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                        for (int m = 0; m < 4; m++) {
+                            const uint32_t a[4] = {fp8x2_to_half2(wl[m] & 0xffffu), fp8x2_to_half2(wh[m] & 0xffffu),
+                                                   fp8x2_to_half2(wl[m] >> 16),     fp8x2_to_half2(wh[m] >> 16)};
+                            const int ks = 4 * j + m;
+                            if (m & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
+                            else       mma_16816(s0, a, qb[ks][0], qb[ks][1]);
+                        }
+                    }
+                }
+
+                // ---- 2. online softmax. This lane: tokens g, g+8 of the group, heads 2qd, 2qd+1.
+                float x[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) x[i] = (s0[i] + s1[i]) * qk_scale;
+                if (grp_valid < 16) {
+                    if (g >= grp_valid)     { x[0] = -INFINITY; x[1] = -INFINITY; }
+                    if (g + 8 >= grp_valid) { x[2] = -INFINITY; x[3] = -INFINITY; }
+                }
+                float mx[2] = {fmaxf(x[0], x[2]), fmaxf(x[1], x[3])};
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+                    mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+                }
+                float alpha[2];
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float m_new = fmaxf(m_run[h], mx[h]);
+                    alpha[h] = exp2f(m_run[h] - m_new);
+                    m_run[h] = m_new;
+                }
+                float pr[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) pr[i] = exp2f(x[i] - m_run[i & 1]);
+                l_run[0] = l_run[0] * alpha[0] + (pr[0] + pr[2]);
+                l_run[1] = l_run[1] * alpha[1] + (pr[1] + pr[3]);
+#pragma unroll
+                for (int mt = 0; mt < 8; mt++) {
+                    acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
+                    acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
+                }
+
+                // ---- 3. O^T += V^T P^T.  P^T's B fragment = transposed 8x8 blocks of the scores.
+                const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));   // tokens 0..7
+                const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));   // tokens 8..15
+                if constexpr (!FP8) {
+                    const int t = grp_row + (lane & 7) + ((lane >> 4) & 1) * 8;
+                    const uint32_t r0 = row_offset<KV>(t, 0, btl), r1 = row_offset<KV>(t, 1, btl);
+                    const int hi = (lane >> 3) & 1;
+#pragma unroll
+                    for (int mt = 0; mt < 8; mt++) {
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(a, v_tile + swz(mt < 4 ? r0 : r1, (mt & 3) * 2 + hi));
+                        mma_16816(acc[mt], a, pb0, pb1);
+                    }
+                } else {
+                    // This lane: tokens 2qd, 2qd+1, 2qd+8, 2qd+9, dims 16g..16g+15.  M-tile mt has
+                    // row g = dim 16g + 2mt and row g+8 = dim 16g + 2mt + 1.
+                    uint32_t vw[4][4];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int t = grp_row + 2 * qd + (r & 1) + (r >> 1) * 8;
+                        const uint4 v = lds128(v_tile + swz(row_offset<KV>(t, 0, btl), g));
+                        vw[r][0] = v.x; vw[r][1] = v.y; vw[r][2] = v.z; vw[r][3] = v.w;
+                    }
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        // bytes [t0 d, t1 d, t0 d+1, t1 d+1] for d = 4w (lo) and 4w+2 (hi)
+                        const uint32_t lo01 = __byte_perm(vw[0][w], vw[1][w], 0x5140u);
+                        const uint32_t hi01 = __byte_perm(vw[0][w], vw[1][w], 0x7362u);
+                        const uint32_t lo23 = __byte_perm(vw[2][w], vw[3][w], 0x5140u);
+                        const uint32_t hi23 = __byte_perm(vw[2][w], vw[3][w], 0x7362u);
+                        const uint32_t a_lo[4] = {fp8x2_to_half2(lo01 & 0xffffu), fp8x2_to_half2(lo01 >> 16),
+                                                  fp8x2_to_half2(lo23 & 0xffffu), fp8x2_to_half2(lo23 >> 16)};
+                        const uint32_t a_hi[4] = {fp8x2_to_half2(hi01 & 0xffffu), fp8x2_to_half2(hi01 >> 16),
+                                                  fp8x2_to_half2(hi23 & 0xffffu), fp8x2_to_half2(hi23 >> 16)};
+                        mma_16816(acc[2 * w],     a_lo, pb0, pb1);
+                        mma_16816(acc[2 * w + 1], a_hi, pb0, pb1);
+                    }
+                }
+            }
+
+            // Release the stage to the producer.
+            if (wrote) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty_bar(stage));
+            consumed++;
+        }
+        if (!alive) break;
+
+        // ---- segment end: merge the warps' softmax states and write the result.
+        {
+            float l[2] = {l_run[0], l_run[1]};
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                l[0] += __shfl_xor_sync(0xffffffffu, l[0], o);
+                l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
+            }
+            const int item = sg.x * p.num_kv_heads + sg.y;
+            const bool whole = p.item_seg_begin[item + 1] - p.item_seg_begin[item] == 1;
+#pragma unroll
+            for (int pass = 0; pass < S::PASSES; pass++) {
+                const int head0 = pass * 4;   // heads [head0, head0 + GROUP_PAD) in this pass
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int head = 2 * qd + h;
+                    if (head < GROUP && head >= head0 && head < head0 + S::GROUP_PAD) {
+                        float* row = w_o + (warp * S::GROUP_PAD + (head - head0)) * OSTRIDE;
+#pragma unroll
+                        for (int mt = 0; mt < 8; mt++) {
+                            if constexpr (FP8) {
+                                row[16 * g + 2 * mt]     = acc[mt][h];
+                                row[16 * g + 2 * mt + 1] = acc[mt][2 + h];
+                            } else {
+                                row[16 * mt + g]     = acc[mt][h];
+                                row[16 * mt + g + 8] = acc[mt][2 + h];
+                            }
+                        }
+                        if (g == 0) { w_m[warp * 8 + head] = m_run[h]; w_l[warp * 8 + head] = l[h]; }
+                    }
+                }
+                if (!consumer_sync()) break;
+                constexpr int HEADS = GROUP < S::GROUP_PAD ? GROUP : S::GROUP_PAD;
+                for (int i = tid; i < HEADS * HEAD_DIM; i += S::CONSUMERS) {
+                    const int hl = i / HEAD_DIM, d = i % HEAD_DIM, hd = head0 + hl;
+                    float m_all = -INFINITY;
+#pragma unroll
+                    for (int w = 0; w < C::WARPS; w++) m_all = fmaxf(m_all, w_m[w * 8 + hd]);
+                    float num = 0.f, den = 0.f;
+#pragma unroll
+                    for (int w = 0; w < C::WARPS; w++) {
+                        const float wt = exp2f(w_m[w * 8 + hd] - m_all);   // 0 for warps that saw no tokens
+                        num = fmaf(wt, w_o[(w * S::GROUP_PAD + hl) * OSTRIDE + d], num);
+                        den = fmaf(wt, w_l[w * 8 + hd], den);
+                    }
+                    const float o = num / den * p.v_scale;
+                    if (whole) {
+                        static_cast<__half*>(p.out)[(static_cast<size_t>(sg.x) * p.num_q_heads + sg.y * GROUP + hd) * HEAD_DIM + d] = __float2half(o);
+                    } else {
+                        const size_t row = static_cast<size_t>(seg) * GROUP + hd;
+                        p.partial_out[row * HEAD_DIM + d] = o;
+                        if (d == 0) p.partial_lse[row] = m_all + log2f(den);
+                    }
+                }
+                if (!consumer_sync()) break;   // scratch is rewritten by the next pass / segment
+            }
+        }
+    }
+}
+
+// ---- merge kernel -------------------------------------------------------------------
+// One warp per (row, query head) whose (row, kv head) was split.  Lanes first run
+// over the segments (max and sum of the base-2 LSE weights by butterfly shuffles),
+// then over the head dimension, four floats per lane, with each segment's weight
+// broadcast by shuffle.  Same arithmetic as merge_segments_kernel
+// (src/decode/decode_kernels.cuh:409-432).
+template<int GROUP>
+__global__ void __launch_bounds__(128)
+merge_segments_kernel(const __grid_constant__ pd_params p)
+{
+    const int lane = threadIdx.x & 31;
+    const int idx  = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (row, q head)
+    if (idx >= p.batch * p.num_q_heads) return;
+    const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
+    const int item = b * p.num_kv_heads + hq / GROUP;
+    const int gq = hq % GROUP;
+    const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
+    if (s1 - s0 <= 1) return;   // written directly by the decode kernel
+
+    float lse_max = -INFINITY;
+    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, p.partial_lse[s * GROUP + gq]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
+
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (int base = s0; base < s1; base += 32) {
+        const int s = base + lane;
+        const float w_mine = s < s1 ? exp2f(p.partial_lse[s * GROUP + gq] - lse_max) : 0.f;
+        const int n = min(32, s1 - base);
+        for (int j = 0; j < n; j++) {
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            const float4 o = *reinterpret_cast<const float4*>(
+                p.partial_out + (static_cast<size_t>(base + j) * GROUP + gq) * HEAD_DIM + lane * 4);
+            num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
+            num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
+            den += w;
+        }
+    }
+    const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
+    const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + (static_cast<size_t>(b) * p.num_q_heads + hq) * HEAD_DIM + lane * 4) = packed;
+}
+
+}  // namespace pdk

@@ -1,0 +1,814 @@
+// libpd_b200.so: host side of the engine and its C ABI (include/pd_b200.h).
+//
+// Host logic here is new code written against the reference's observable
+// behaviour (src/decode/decode.cu, src/decode/paged_kv_cache.cu): same plan for
+// the same (tile, num_ctas), same allocator decisions, same cache bytes.
+
+#include "pd_b200.h"
+
+#include "append_kernel.cuh"
+#include "decode_kernel.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <numeric>
+#include <random>
+#include <string>
+#include <vector>
+
+namespace {
+
+// ---- errors -----------------------------------------------------------------------
+
+thread_local std::string g_last_error;
+
+int set_error(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    std::vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define PD_CUDA(expr)                                                                      \
+    do {                                                                                   \
+        cudaError_t e_ = (expr);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return set_error(PD_CUDA_ERROR, "CUDA error %s at %s:%d: %s", cudaGetErrorName(e_), \
+                             __FILE__, __LINE__, cudaGetErrorString(e_));                  \
+    } while (0)
+
+// ---- kernel variants ------------------------------------------------------------------
+// A variant fixes the CTA shape and pipeline depth for both cache dtypes.  Variant 0
+// is the default; the others exist for tuning runs (pd_set_kernel_variant).
+
+template<int V, typename KV> struct VariantConfig;
+// 4 consumer warps, 64-token tiles, 96 KB of pipeline, two CTAs per SM.
+template<> struct VariantConfig<0, __half>        { using type = pdk::Config<4, 1, 3, 2>; };
+template<> struct VariantConfig<0, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 6, 2>; };
+// 8 consumer warps, 128-token tiles, 192 KB of pipeline, one CTA per SM.
+template<> struct VariantConfig<1, __half>        { using type = pdk::Config<8, 1, 3, 1>; };
+template<> struct VariantConfig<1, __nv_fp8_e4m3> { using type = pdk::Config<8, 1, 6, 1>; };
+// 4 consumer warps, 64-token tiles, deep pipeline, one CTA per SM.
+template<> struct VariantConfig<2, __half>        { using type = pdk::Config<4, 1, 6, 1>; };
+template<> struct VariantConfig<2, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 12, 1>; };
+// 8 consumer warps on 64-token tiles is not expressible (one group per warp), so
+// variant 3 gives each of 4 warps two groups: 128-token tiles, one CTA per SM.
+template<> struct VariantConfig<3, __half>        { using type = pdk::Config<4, 2, 3, 1>; };
+template<> struct VariantConfig<3, __nv_fp8_e4m3> { using type = pdk::Config<4, 2, 6, 1>; };
+constexpr int NUM_VARIANTS = 4;
+
+struct KernelInfo {
+    const void* fn;
+    int tile, threads, smem, per_sm;
+    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, cudaStream_t);
+    void (*merge)(const pd_params&, cudaStream_t);
+};
+
+template<typename KV, int GROUP, typename C>
+void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl,
+                   unsigned* status, cudaStream_t stream) {
+    using S = pdk::Shape<KV, GROUP, C>;
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status);
+}
+template<int GROUP>
+void launch_merge(const pd_params& p, cudaStream_t stream) {
+    const int rows = p.batch * p.num_q_heads;
+    pdk::merge_segments_kernel<GROUP><<<(rows + 3) / 4, 128, 0, stream>>>(p);
+}
+
+template<typename KV, int GROUP, int V>
+KernelInfo make_info() {
+    using C = typename VariantConfig<V, KV>::type;
+    using S = pdk::Shape<KV, GROUP, C>;
+    return KernelInfo{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
+                      S::SMEM_BYTES, C::MIN_CTAS, &launch_decode<KV, GROUP, C>, &launch_merge<GROUP>};
+}
+
+template<typename KV, int V>
+const KernelInfo* info_by_group(int group) {
+    static const KernelInfo t[4] = {make_info<KV, 1, V>(), make_info<KV, 2, V>(), make_info<KV, 4, V>(),
+                                    make_info<KV, 8, V>()};
+    switch (group) {
+        case 1: return &t[0];
+        case 2: return &t[1];
+        case 4: return &t[2];
+        case 8: return &t[3];
+    }
+    return nullptr;
+}
+
+template<typename KV>
+const KernelInfo* info_by_variant(int variant, int group) {
+    switch (variant) {
+        case 0: return info_by_group<KV, 0>(group);
+        case 1: return info_by_group<KV, 1>(group);
+        case 2: return info_by_group<KV, 2>(group);
+        case 3: return info_by_group<KV, 3>(group);
+    }
+    return nullptr;
+}
+
+int g_variant = -1;
+std::once_flag g_variant_once;
+int current_variant() {
+    std::call_once(g_variant_once, [] {
+        if (g_variant >= 0) return;
+        const char* e = std::getenv("PD_B200_VARIANT");
+        const int v = e ? std::atoi(e) : 0;
+        g_variant = (v >= 0 && v < NUM_VARIANTS) ? v : 0;
+    });
+    return g_variant;
+}
+
+// Same argument checks, in the same order, as the reference's dispatch
+// (src/decode/decode.cu:18-39): head_dim first, then the group size.
+int find_kernel(int dtype, int head_dim, int group, const KernelInfo** out) {
+    if (dtype != PD_FP16 && dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "unsupported KV dtype %d", dtype);
+    if (head_dim != 128) return set_error(PD_INVALID_ARGUMENT, "unsupported head_dim %d", head_dim);
+    const KernelInfo* k = dtype == PD_FP16 ? info_by_variant<__half>(current_variant(), group)
+                                           : info_by_variant<__nv_fp8_e4m3>(current_variant(), group);
+    if (!k) return set_error(PD_INVALID_ARGUMENT, "unsupported GQA group size %d", group);
+    *out = k;
+    return PD_OK;
+}
+
+// cudaFuncSetAttribute once per (kernel, device).
+std::mutex g_cfg_mutex;
+std::vector<std::pair<const void*, int>> g_configured;
+int configure(const KernelInfo* k) {
+    int dev = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_cfg_mutex);
+    for (auto& c : g_configured) if (c.first == k->fn && c.second == dev) return PD_OK;
+    PD_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->smem));
+    g_configured.emplace_back(k->fn, dev);
+    return PD_OK;
+}
+
+// ---- per-device status word -----------------------------------------------------------
+
+constexpr int MAX_DEVICES = 64;
+unsigned* g_status[MAX_DEVICES] = {};
+std::mutex g_status_mutex;
+int status_word(unsigned** out) {
+    int dev = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return set_error(PD_INTERNAL, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (!g_status[dev]) {
+        PD_CUDA(cudaMalloc(&g_status[dev], sizeof(unsigned)));
+        PD_CUDA(cudaMemset(g_status[dev], 0, sizeof(unsigned)));
+    }
+    *out = g_status[dev];
+    return PD_OK;
+}
+
+// ---- TMA descriptors --------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+int encode_fn(EncodeTiledFn* out) {
+    std::call_once(g_encode_once, [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    });
+    if (!g_encode) return set_error(PD_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+    *out = g_encode;
+    return PD_OK;
+}
+
+unsigned gcd_u(unsigned a, unsigned b) { while (b) { const unsigned t = a % b; a = b; b = t; } return a; }
+
+// Tensor map over one pool [page][kv head][token][dim].
+//   fp16: 5-D  (64 dims, token, panel, kv head, page), box (64, 2^btl, 2, 1, 1)
+//   fp8 : 4-D  (128 dims, token, kv head, page),       box (128, 2^btl, 1, 1)
+// so a box lands in shared memory as [panel][token][128 bytes] under the 128-byte swizzle.
+int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages, int num_kv_heads,
+                    int page_size, int btl) {
+    EncodeTiledFn enc;
+    if (int rc = encode_fn(&enc)) return rc;
+    if (reinterpret_cast<uintptr_t>(pool) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "KV pool pointer must be 16-byte aligned");
+    const cuuint64_t pages = num_pages > 0 ? static_cast<cuuint64_t>(num_pages) : (1ull << 31);
+    const cuuint64_t row = dtype == PD_FP16 ? 256 : 128;
+    CUresult r;
+    if (dtype == PD_FP16) {
+        const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
+        const cuuint64_t strides[4] = {row, 128, row * page_size, row * page_size * num_kv_heads};
+        const cuuint32_t box[5]     = {64, 1u << btl, 2, 1, 1};
+        const cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
+        r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(pool), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t dims[4]    = {128, static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(num_kv_heads), pages};
+        const cuuint64_t strides[3] = {row, row * page_size, row * page_size * num_kv_heads};
+        const cuuint32_t box[4]     = {128, 1u << btl, 1, 1};
+        const cuuint32_t estr[4]    = {1, 1, 1, 1};
+        r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(pool), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return set_error(PD_CUDA_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return PD_OK;
+}
+
+// ---- planner ------------------------------------------------------------------------------
+
+// The flat list of (row, kv head, tile) work units is cut into num_ctas contiguous
+// runs of `per` units; each maximal run of one (row, head) inside a CTA's share is a
+// segment.  Produces exactly the plan of decode::make_plan (src/decode/decode.cu:65-108)
+// for the same tile and num_ctas.
+int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads, int num_ctas,
+               pd_plan** out);
+
+}  // namespace
+
+struct pd_plan {
+    int num_ctas = 0;
+    int tile     = 0;
+    int num_items = 0;
+    std::vector<int> segments;        // 4 ints each
+    std::vector<int> cta_seg_begin;
+    std::vector<int> item_seg_begin;
+};
+
+namespace {
+
+int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads, int num_ctas,
+               pd_plan** out) {
+    if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    if (tile <= 0 || num_ctas <= 0 || batch < 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: tile, num_ctas must be positive");
+    long long total = 0;
+    for (int b = 0; b < batch; b++) {
+        if (seq_lens[b] <= 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: every sequence needs at least one token");
+        total += static_cast<long long>((seq_lens[b] + tile - 1) / tile) * num_kv_heads;
+    }
+    pd_plan* plan = new pd_plan();
+    plan->tile = tile;
+    plan->num_items = batch * num_kv_heads;
+    plan->item_seg_begin.assign(plan->num_items + 1, 0);
+    if (total == 0) {   // empty batch: nothing to launch
+        plan->cta_seg_begin.assign(1, 0);
+        *out = plan;
+        return PD_OK;
+    }
+    const long long per = (total + num_ctas - 1) / num_ctas;   // work units per CTA
+    plan->num_ctas = static_cast<int>((total + per - 1) / per);
+    plan->cta_seg_begin.reserve(plan->num_ctas + 1);
+    plan->cta_seg_begin.push_back(0);
+    long long room = per;                                      // units the current CTA can still take
+    for (int item = 0; item < plan->num_items; item++) {
+        const int b = item / num_kv_heads, h = item % num_kv_heads;
+        const int len = seq_lens[b];
+        const int tiles = (len + tile - 1) / tile;
+        int first = 0;
+        while (first < tiles) {
+            if (room == 0) {
+                plan->cta_seg_begin.push_back(static_cast<int>(plan->segments.size() / 4));
+                room = per;
+            }
+            const int take = static_cast<int>(std::min<long long>(room, tiles - first));
+            const int seg[4] = {b, h, first * tile, std::min((first + take) * tile, len)};
+            plan->segments.insert(plan->segments.end(), seg, seg + 4);
+            plan->item_seg_begin[item + 1] = plan->item_seg_begin[item + 1] + 1;
+            first += take;
+            room -= take;
+        }
+    }
+    plan->cta_seg_begin.push_back(static_cast<int>(plan->segments.size() / 4));
+    for (int i = 0; i < plan->num_items; i++) plan->item_seg_begin[i + 1] += plan->item_seg_begin[i];
+    if (static_cast<int>(plan->cta_seg_begin.size()) != plan->num_ctas + 1) {
+        delete plan;
+        return set_error(PD_INTERNAL, "planner produced an inconsistent CTA table");
+    }
+    *out = plan;
+    return PD_OK;
+}
+
+// Host-side validation of a plan against the lengths it was made for; every index
+// the kernels will dereference is checked here so the device never reads out of range.
+int validate_plan(const pd_plan& plan, const int* seq_lens, int batch, int num_kv_heads) {
+    const int nseg = static_cast<int>(plan.segments.size() / 4);
+    if (static_cast<int>(plan.cta_seg_begin.size()) != plan.num_ctas + 1) return set_error(PD_INTERNAL, "plan: cta table size");
+    for (int c = 0; c < plan.num_ctas; c++)
+        if (plan.cta_seg_begin[c] > plan.cta_seg_begin[c + 1]) return set_error(PD_INTERNAL, "plan: cta table not monotone");
+    if (plan.cta_seg_begin.front() != 0 || plan.cta_seg_begin.back() != nseg) return set_error(PD_INTERNAL, "plan: cta table ends");
+    for (int s = 0; s < nseg; s++) {
+        const int* g = &plan.segments[4 * s];
+        if (g[0] < 0 || g[0] >= batch || g[1] < 0 || g[1] >= num_kv_heads || g[2] < 0 || g[2] >= g[3] ||
+            g[3] > seq_lens[g[0]] || g[2] % plan.tile != 0)
+            return set_error(PD_INTERNAL, "plan: segment %d out of range", s);
+    }
+    return PD_OK;
+}
+
+}  // namespace
+
+// ---- DevicePlan ---------------------------------------------------------------------------------
+
+struct pd_device_plan {
+    int device = -1;
+    void*  arena = nullptr;      // segments | cta_seg_begin | item_seg_begin, one allocation
+    size_t arena_cap = 0;
+    void*  staging = nullptr;    // pinned host mirror of the arena
+    size_t staging_cap = 0;
+    cudaEvent_t staged = nullptr;   // completion of the last upload out of `staging`
+    float* partial = nullptr;
+    size_t partial_cap = 0;      // floats
+    // views into the arena
+    const void* segments = nullptr;
+    const int*  cta_seg_begin = nullptr;
+    const int*  item_seg_begin = nullptr;
+    float* partial_out = nullptr;
+    float* partial_lse = nullptr;
+    int    num_ctas = 0;
+    int    needs_merge = 0;
+    int    num_segments = 0;
+};
+
+// ---- cache -----------------------------------------------------------------------------------------
+
+struct pd_cache {
+    pd_cache_config cfg{};
+    void* d_k = nullptr;
+    void* d_v = nullptr;
+    int*  d_block_table = nullptr;
+    int*  d_seq_lens = nullptr;
+    int*  d_slot_ids = nullptr;
+    size_t slot_ids_cap = 0;
+    pd_plan* plan = nullptr;
+    pd_device_plan* device_plan = nullptr;
+    int plan_batch = 0, plan_num_q_heads = 0;
+    std::vector<int> free_pages;
+    std::vector<std::vector<int>> tables;
+    std::vector<int> seq_lens;
+    std::vector<char> occupied;
+};
+
+extern "C" {
+
+const char* pd_last_error(void) { return g_last_error.c_str(); }
+const char* pd_version(void) { return "pd_b200 0.1 (sm_100a)"; }
+
+int pd_kv_dtype_bytes(int dtype) { return dtype == PD_FP16 ? 2 : 1; }
+const char* pd_kv_dtype_name(int dtype) { return dtype == PD_FP16 ? "fp16" : "fp8_e4m3"; }
+
+int pd_set_kernel_variant(int variant) {
+    if (variant < 0 || variant >= NUM_VARIANTS) return set_error(PD_INVALID_ARGUMENT, "kernel variant %d does not exist", variant);
+    current_variant();   // consume the once-flag so the environment cannot override later
+    g_variant = variant;
+    return PD_OK;
+}
+int pd_kernel_variant(void) { return current_variant(); }
+
+int pd_tile_tokens(int dtype, int head_dim, int group, int* out) {
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
+    *out = k->tile;
+    return PD_OK;
+}
+
+int pd_wave_ctas(int dtype, int head_dim, int group, int* out) {
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
+    if (int rc = configure(k)) return rc;
+    int dev = 0, sms = 0, resident = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    PD_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PD_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, k->fn, k->threads, k->smem));
+    *out = sms * resident;
+    return PD_OK;
+}
+
+// One wave at the residency the variant was shaped for (never more than fits).
+int pd_default_ctas(int dtype, int head_dim, int group, int* out) {
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
+    int wave = 0;
+    if (int rc = pd_wave_ctas(dtype, head_dim, group, &wave)) return rc;
+    int dev = 0, sms = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    PD_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    *out = std::min(wave, sms * k->per_sm);
+    if (*out <= 0) return set_error(PD_CUDA_ERROR, "decode kernel does not fit on this device");
+    return PD_OK;
+}
+
+int pd_make_plan_tiled(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                       int num_ctas, pd_plan** out) {
+    if (!out || (batch > 0 && !seq_lens)) return set_error(PD_INVALID_ARGUMENT, "make_plan: null argument");
+    return build_plan(tile, seq_lens, batch, num_q_heads, num_kv_heads, num_ctas, out);
+}
+
+int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                 int head_dim, int num_ctas, pd_plan** out) {
+    if (!out || (batch > 0 && !seq_lens)) return set_error(PD_INVALID_ARGUMENT, "make_plan: null argument");
+    if (num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    const int group = num_q_heads / num_kv_heads;
+    int tile = 0;
+    if (int rc = pd_tile_tokens(dtype, head_dim, group, &tile)) return rc;
+    if (num_ctas <= 0)
+        if (int rc = pd_default_ctas(dtype, head_dim, group, &num_ctas)) return rc;
+    return build_plan(tile, seq_lens, batch, num_q_heads, num_kv_heads, num_ctas, out);
+}
+
+void pd_plan_free(pd_plan* plan) { delete plan; }
+int pd_plan_num_ctas(const pd_plan* p) { return p->num_ctas; }
+int pd_plan_tile(const pd_plan* p) { return p->tile; }
+int pd_plan_num_segments(const pd_plan* p) { return static_cast<int>(p->segments.size() / 4); }
+int pd_plan_num_items(const pd_plan* p) { return p->num_items; }
+const int* pd_plan_segments(const pd_plan* p) { return p->segments.data(); }
+const int* pd_plan_cta_seg_begin(const pd_plan* p) { return p->cta_seg_begin.data(); }
+const int* pd_plan_item_seg_begin(const pd_plan* p) { return p->item_seg_begin.data(); }
+
+// ---- DevicePlan -------------------------------------------------------------------------------------
+
+int pd_device_plan_create(pd_device_plan** out) {
+    if (!out) return set_error(PD_INVALID_ARGUMENT, "device_plan_create: null argument");
+    *out = new pd_device_plan();
+    return PD_OK;
+}
+
+void pd_device_plan_destroy(pd_device_plan* dp) {
+    if (!dp) return;
+    if (dp->staged) { cudaEventSynchronize(dp->staged); cudaEventDestroy(dp->staged); }
+    cudaFree(dp->arena);
+    cudaFree(dp->partial);
+    cudaFreeHost(dp->staging);
+    delete dp;
+}
+
+int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, int head_dim, void* stream_) {
+    if (!dp || !plan) return set_error(PD_INVALID_ARGUMENT, "device_plan_upload: null argument");
+    if (group <= 0 || head_dim <= 0) return set_error(PD_INVALID_ARGUMENT, "device_plan_upload: group and head_dim must be positive");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const size_t nseg = plan->segments.size() / 4;
+    auto round16 = [](size_t x) { return (x + 15) & ~static_cast<size_t>(15); };
+    const size_t seg_bytes  = round16(sizeof(int) * plan->segments.size());
+    const size_t cta_bytes  = round16(sizeof(int) * plan->cta_seg_begin.size());
+    const size_t item_bytes = round16(sizeof(int) * plan->item_seg_begin.size());
+    const size_t total = seg_bytes + cta_bytes + item_bytes;
+    if (total > dp->arena_cap) {
+        PD_CUDA(cudaFree(dp->arena));
+        dp->arena = nullptr; dp->arena_cap = 0;
+        PD_CUDA(cudaMalloc(&dp->arena, total));
+        dp->arena_cap = total;
+    }
+    if (!dp->staged) PD_CUDA(cudaEventCreateWithFlags(&dp->staged, cudaEventDisableTiming));
+    else PD_CUDA(cudaEventSynchronize(dp->staged));   // the previous upload still reads `staging`
+    if (total > dp->staging_cap) {
+        PD_CUDA(cudaFreeHost(dp->staging));
+        dp->staging = nullptr; dp->staging_cap = 0;
+        PD_CUDA(cudaMallocHost(&dp->staging, total));
+        dp->staging_cap = total;
+    }
+    char* h = static_cast<char*>(dp->staging);
+    std::memcpy(h, plan->segments.data(), sizeof(int) * plan->segments.size());
+    std::memcpy(h + seg_bytes, plan->cta_seg_begin.data(), sizeof(int) * plan->cta_seg_begin.size());
+    std::memcpy(h + seg_bytes + cta_bytes, plan->item_seg_begin.data(), sizeof(int) * plan->item_seg_begin.size());
+    if (total) PD_CUDA(cudaMemcpyAsync(dp->arena, dp->staging, total, cudaMemcpyHostToDevice, stream));
+    PD_CUDA(cudaEventRecord(dp->staged, stream));
+
+    // Workspace for split rows: [segments][group][head_dim] outputs then [segments][group] LSEs.
+    const size_t rows = nseg * group;
+    const size_t need = rows * (head_dim + 1);
+    if (need > dp->partial_cap) {
+        PD_CUDA(cudaFree(dp->partial));
+        dp->partial = nullptr; dp->partial_cap = 0;
+        PD_CUDA(cudaMalloc(&dp->partial, sizeof(float) * need));
+        dp->partial_cap = need;
+    }
+    char* a = static_cast<char*>(dp->arena);
+    dp->segments       = a;
+    dp->cta_seg_begin  = reinterpret_cast<const int*>(a + seg_bytes);
+    dp->item_seg_begin = reinterpret_cast<const int*>(a + seg_bytes + cta_bytes);
+    dp->partial_out    = dp->partial;
+    dp->partial_lse    = dp->partial ? dp->partial + rows * head_dim : nullptr;
+    dp->num_ctas       = plan->num_ctas;
+    dp->num_segments   = static_cast<int>(nseg);
+    dp->needs_merge    = static_cast<int>(nseg) > plan->num_items ? 1 : 0;
+    return PD_OK;
+}
+
+int pd_device_plan_bind(const pd_device_plan* dp, pd_params* p) {
+    if (!dp || !p) return set_error(PD_INVALID_ARGUMENT, "device_plan_bind: null argument");
+    p->segments       = dp->segments;
+    p->cta_seg_begin  = dp->cta_seg_begin;
+    p->item_seg_begin = dp->item_seg_begin;
+    p->num_ctas       = dp->num_ctas;
+    p->needs_merge    = dp->needs_merge;
+    p->partial_out    = dp->partial_out;
+    p->partial_lse    = dp->partial_lse;
+    return PD_OK;
+}
+
+// ---- decode -----------------------------------------------------------------------------------------------
+
+int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream_) {
+    if (!p) return set_error(PD_INVALID_ARGUMENT, "paged_decode: null params");
+    if (p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, p->head_dim, p->num_q_heads / p->num_kv_heads, &k)) return rc;
+    if (p->page_size <= 0) return set_error(PD_INVALID_ARGUMENT, "page_size must be positive");
+    if (p->num_ctas <= 0 || p->batch <= 0) return PD_OK;   // empty plan: nothing to do
+    if (!p->q || !p->out || !p->k_cache || !p->v_cache || !p->block_table || !p->segments || !p->cta_seg_begin ||
+        !p->item_seg_begin)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode: null device pointer");
+    if (p->needs_merge && (!p->partial_out || !p->partial_lse))
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode: split rows need the partial workspace");
+    if (int rc = configure(k)) return rc;
+    unsigned* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+
+    // A box is the largest run of tokens that never straddles a page or a tile.
+    const unsigned box_tokens = gcd_u(static_cast<unsigned>(p->page_size), static_cast<unsigned>(k->tile));
+    int btl = 0;
+    while ((1u << (btl + 1)) <= box_tokens) btl++;
+    CUtensorMap k_map, v_map;
+    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    k->launch(*p, k_map, v_map, btl, status, stream);
+    PD_CUDA(cudaGetLastError());
+    if (p->needs_merge) {
+        k->merge(*p, stream);
+        PD_CUDA(cudaGetLastError());
+    }
+    return PD_OK;
+}
+
+int pd_paged_decode(int dtype, const pd_params* p, void* stream) {
+    return pd_paged_decode_bounded(dtype, p, 0, stream);
+}
+
+int pd_kernel_status(void* stream, unsigned* out) {
+    if (!out) return set_error(PD_INVALID_ARGUMENT, "kernel_status: null argument");
+    unsigned* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    PD_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    PD_CUDA(cudaMemcpy(out, status, sizeof(unsigned), cudaMemcpyDeviceToHost));
+    if (*out) {
+        PD_CUDA(cudaMemset(status, 0, sizeof(unsigned)));
+        return set_error(PD_KERNEL_TIMEOUT, "decode kernel: bounded wait %u expired in CTA %u", *out >> 24, *out & 0xffffffu);
+    }
+    return PD_OK;
+}
+
+// ---- append ------------------------------------------------------------------------------------------------
+
+int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
+                     const int* d_block_table_row, int start_pos, int n, int num_kv_heads, int head_dim,
+                     int page_size, float k_scale, float v_scale, void* stream_) {
+    if (dtype != PD_FP16 && dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "unsupported KV dtype %d", dtype);
+    if (head_dim != 128) return set_error(PD_INVALID_ARGUMENT, "append: head_dim must be 128");
+    if (n <= 0) return PD_OK;
+    if (!d_k || !d_v || !k_cache || !v_cache || !d_block_table_row || num_kv_heads <= 0 || page_size <= 0 || start_pos < 0)
+        return set_error(PD_INVALID_ARGUMENT, "append: bad argument");
+    if ((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v) | reinterpret_cast<uintptr_t>(k_cache) |
+         reinterpret_cast<uintptr_t>(v_cache)) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "append: K/V buffers must be 16-byte aligned");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    pdk::AppendJob job{static_cast<const __half*>(d_k), static_cast<const __half*>(d_v), d_block_table_row, start_pos, n, 0};
+    const long long units = static_cast<long long>(n) * num_kv_heads * 16;
+    const int blocks = static_cast<int>(std::min<long long>((units + 255) / 256, 148 * 16));
+    if (dtype == PD_FP16)
+        pdk::append_kernel<false><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size, 1.f, 1.f);
+    else
+        pdk::append_kernel<true><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size,
+                                                             1.f / k_scale, 1.f / v_scale);
+    PD_CUDA(cudaGetLastError());
+    return PD_OK;
+}
+
+// ---- PagedKVCache ---------------------------------------------------------------------------------------------
+
+size_t pd_cache_bytes_per_page(const pd_cache_config* cfg) {
+    return 2ull * cfg->num_kv_heads * cfg->page_size * cfg->head_dim * pd_kv_dtype_bytes(cfg->dtype);
+}
+
+int pd_cache_pages_for_budget(const pd_cache_config* cfg, size_t budget_bytes) {
+    return static_cast<int>(budget_bytes / pd_cache_bytes_per_page(cfg));
+}
+
+void pd_cache_destroy(pd_cache* c) {
+    if (!c) return;
+    cudaFree(c->d_k);
+    cudaFree(c->d_v);
+    cudaFree(c->d_block_table);
+    cudaFree(c->d_seq_lens);
+    cudaFree(c->d_slot_ids);
+    pd_plan_free(c->plan);
+    pd_device_plan_destroy(c->device_plan);
+    delete c;
+}
+
+int pd_cache_create(const pd_cache_config* cfg, pd_cache** out) {
+    if (!cfg || !out) return set_error(PD_INVALID_ARGUMENT, "PagedKVCache: null argument");
+    if (cfg->num_pages <= 0 || cfg->page_size <= 0 || cfg->num_kv_heads <= 0 || cfg->max_slots <= 0 ||
+        cfg->max_pages_per_slot <= 0)
+        return set_error(PD_INVALID_ARGUMENT, "PagedKVCache: all sizes must be positive");
+    if (cfg->head_dim != 128) return set_error(PD_INVALID_ARGUMENT, "PagedKVCache: head_dim must be 128");
+    if (cfg->dtype != PD_FP16 && cfg->dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "PagedKVCache: unsupported KV dtype");
+    pd_cache* c = new pd_cache();
+    c->cfg = *cfg;
+    c->tables.resize(cfg->max_slots);
+    c->seq_lens.assign(cfg->max_slots, 0);
+    c->occupied.assign(cfg->max_slots, 0);
+    auto fail = [&](int rc) { pd_cache_destroy(c); return rc; };
+#define PD_CACHE_CUDA(expr)                                                                           \
+    do {                                                                                              \
+        cudaError_t e_ = (expr);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(set_error(PD_CUDA_ERROR, "CUDA error %s at %s:%d: %s", cudaGetErrorName(e_),  \
+                                  __FILE__, __LINE__, cudaGetErrorString(e_)));                       \
+    } while (0)
+    const size_t half_bytes = pd_cache_bytes_per_page(cfg) / 2 * cfg->num_pages;
+    const size_t table_bytes = sizeof(int) * static_cast<size_t>(cfg->max_slots) * cfg->max_pages_per_slot;
+    PD_CACHE_CUDA(cudaMalloc(&c->d_k, half_bytes));
+    PD_CACHE_CUDA(cudaMalloc(&c->d_v, half_bytes));
+    // Pools start as zeros: the decode kernel copies whole pages, and bytes a sequence
+    // never wrote must not decode to NaN.
+    PD_CACHE_CUDA(cudaMemset(c->d_k, 0, half_bytes));
+    PD_CACHE_CUDA(cudaMemset(c->d_v, 0, half_bytes));
+    PD_CACHE_CUDA(cudaMalloc(&c->d_block_table, table_bytes));
+    PD_CACHE_CUDA(cudaMalloc(&c->d_seq_lens, sizeof(int) * cfg->max_slots));
+    PD_CACHE_CUDA(cudaMemset(c->d_block_table, 0, table_bytes));
+    PD_CACHE_CUDA(cudaMemset(c->d_seq_lens, 0, sizeof(int) * cfg->max_slots));
+#undef PD_CACHE_CUDA
+    if (int rc = pd_device_plan_create(&c->device_plan)) return fail(rc);
+    // Pages are taken from the back of the list; page 0 goes out first.
+    c->free_pages.resize(cfg->num_pages);
+    for (int i = 0; i < cfg->num_pages; i++) c->free_pages[i] = cfg->num_pages - 1 - i;
+    *out = c;
+    return PD_OK;
+}
+
+int pd_cache_admit(pd_cache* c) {
+    for (int s = 0; s < c->cfg.max_slots; s++)
+        if (!c->occupied[s]) {
+            c->occupied[s] = 1;
+            c->seq_lens[s] = 0;
+            return s;
+        }
+    return -1;
+}
+
+int pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, int n, void* stream_) {
+    if (!c || slot < 0 || slot >= c->cfg.max_slots || !c->occupied[slot])
+        return set_error(PD_INVALID_ARGUMENT, "append: slot is not admitted");
+    if (n <= 0) return PD_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int ps = c->cfg.page_size;
+    const int old_len = c->seq_lens[slot];
+    const int new_len = old_len + n;
+    const int have = static_cast<int>(c->tables[slot].size());
+    const int need = (new_len + ps - 1) / ps;
+    if (need > c->cfg.max_pages_per_slot) return set_error(PD_LENGTH_ERROR, "append: sequence exceeds max_pages_per_slot");
+    if (need - have > static_cast<int>(c->free_pages.size()))
+        return set_error(PD_OUT_OF_PAGES, "append: out of pages");
+    for (int i = have; i < need; i++) {
+        c->tables[slot].push_back(c->free_pages.back());
+        c->free_pages.pop_back();
+    }
+    int* row = c->d_block_table + static_cast<size_t>(slot) * c->cfg.max_pages_per_slot;
+    // Pageable-source copies are staged by the driver before they return.
+    if (need > have)
+        PD_CUDA(cudaMemcpyAsync(row + have, c->tables[slot].data() + have, sizeof(int) * (need - have),
+                                cudaMemcpyHostToDevice, stream));
+    c->seq_lens[slot] = new_len;
+    PD_CUDA(cudaMemcpyAsync(c->d_seq_lens + slot, &c->seq_lens[slot], sizeof(int), cudaMemcpyHostToDevice, stream));
+    if (int rc = pd_append_tokens(c->cfg.dtype, d_k, d_v, c->d_k, c->d_v, row, old_len, n, c->cfg.num_kv_heads,
+                                  c->cfg.head_dim, ps, c->cfg.k_scale, c->cfg.v_scale, stream))
+        return rc;
+    // As in the reference (src/decode/paged_kv_cache.cu:133-134) the call returns with the tokens in place.
+    PD_CUDA(cudaStreamSynchronize(stream));
+    return PD_OK;
+}
+
+int pd_cache_release(pd_cache* c, int slot) {
+    if (!c || slot < 0 || slot >= c->cfg.max_slots || !c->occupied[slot])
+        return set_error(PD_INVALID_ARGUMENT, "release: slot is not admitted");
+    for (int page : c->tables[slot]) c->free_pages.push_back(page);   // in table order
+    c->tables[slot].clear();
+    c->seq_lens[slot] = 0;
+    c->occupied[slot] = 0;
+    PD_CUDA(cudaMemset(c->d_seq_lens + slot, 0, sizeof(int)));
+    return PD_OK;
+}
+
+void pd_cache_shuffle_free_pages(pd_cache* c, unsigned seed) {
+    std::mt19937 rng(seed);
+    std::shuffle(c->free_pages.begin(), c->free_pages.end(), rng);
+}
+
+int pd_cache_params(const pd_cache* c, pd_params* p) {
+    if (!c || !p) return set_error(PD_INVALID_ARGUMENT, "params: null argument");
+    std::memset(p, 0, sizeof *p);
+    const bool fp8 = c->cfg.dtype == PD_FP8_E4M3;
+    p->k_cache            = c->d_k;
+    p->v_cache            = c->d_v;
+    p->block_table        = c->d_block_table;
+    p->seq_lens           = c->d_seq_lens;
+    p->block_table_stride = c->cfg.max_pages_per_slot;
+    p->num_kv_heads       = c->cfg.num_kv_heads;
+    p->head_dim           = c->cfg.head_dim;
+    p->page_size          = c->cfg.page_size;
+    p->sm_scale           = 1.0f / std::sqrt(static_cast<float>(c->cfg.head_dim));
+    p->k_scale            = fp8 ? c->cfg.k_scale : 1.0f;
+    p->v_scale            = fp8 ? c->cfg.v_scale : 1.0f;
+    return PD_OK;
+}
+
+int pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads, int num_ctas, void* stream_) {
+    if (!c || (num_slots > 0 && !slots)) return set_error(PD_INVALID_ARGUMENT, "plan: null argument");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    std::vector<int> lens(num_slots);
+    for (int i = 0; i < num_slots; i++) {
+        if (slots[i] < 0 || slots[i] >= c->cfg.max_slots || !c->occupied[slots[i]])
+            return set_error(PD_INVALID_ARGUMENT, "plan: slot is not admitted");
+        lens[i] = c->seq_lens[slots[i]];
+    }
+    pd_plan* plan = nullptr;
+    if (int rc = pd_make_plan(c->cfg.dtype, lens.data(), num_slots, num_q_heads, c->cfg.num_kv_heads, c->cfg.head_dim,
+                              num_ctas, &plan))
+        return rc;
+    if (int rc = validate_plan(*plan, lens.data(), num_slots, c->cfg.num_kv_heads)) { pd_plan_free(plan); return rc; }
+    pd_plan_free(c->plan);
+    c->plan = plan;
+    if (int rc = pd_device_plan_upload(c->device_plan, plan, num_q_heads / c->cfg.num_kv_heads, c->cfg.head_dim, stream))
+        return rc;
+    if (static_cast<size_t>(num_slots) > c->slot_ids_cap) {
+        PD_CUDA(cudaFree(c->d_slot_ids));
+        c->d_slot_ids = nullptr; c->slot_ids_cap = 0;
+        PD_CUDA(cudaMalloc(&c->d_slot_ids, sizeof(int) * num_slots));
+        c->slot_ids_cap = num_slots;
+    }
+    if (num_slots)
+        PD_CUDA(cudaMemcpyAsync(c->d_slot_ids, slots, sizeof(int) * num_slots, cudaMemcpyHostToDevice, stream));
+    c->plan_batch = num_slots;
+    c->plan_num_q_heads = num_q_heads;
+    return PD_OK;
+}
+
+int pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream) {
+    if (!c) return set_error(PD_INVALID_ARGUMENT, "run: null cache");
+    if (!c->plan) return set_error(PD_INVALID_ARGUMENT, "run: no plan; call plan() first");
+    pd_params p;
+    pd_cache_params(c, &p);
+    p.q = d_q;
+    p.out = d_out;
+    p.slot_ids = c->d_slot_ids;
+    p.batch = c->plan_batch;
+    p.num_q_heads = c->plan_num_q_heads;
+    pd_device_plan_bind(c->device_plan, &p);
+    return pd_paged_decode_bounded(c->cfg.dtype, &p, c->cfg.num_pages, stream);
+}
+
+int pd_cache_decode(pd_cache* c, const void* d_q, void* d_out, int batch, int num_q_heads, int num_ctas, void* stream) {
+    if (!c || batch < 0) return set_error(PD_INVALID_ARGUMENT, "decode: bad argument");
+    std::vector<int> slots(batch);
+    std::iota(slots.begin(), slots.end(), 0);
+    if (int rc = pd_cache_plan(c, slots.data(), batch, num_q_heads, num_ctas, stream)) return rc;
+    return pd_cache_run(c, d_q, d_out, stream);
+}
+
+const pd_plan* pd_cache_last_plan(const pd_cache* c) { return c->plan; }
+int pd_cache_seq_len(const pd_cache* c, int slot) { return c->seq_lens[slot]; }
+int pd_cache_occupied(const pd_cache* c, int slot) { return c->occupied[slot]; }
+int pd_cache_free_pages(const pd_cache* c) { return static_cast<int>(c->free_pages.size()); }
+int pd_cache_max_seq_len(const pd_cache* c) { return *std::max_element(c->seq_lens.begin(), c->seq_lens.end()); }
+size_t pd_cache_total_bytes(const pd_cache* c) { return pd_cache_bytes_per_page(&c->cfg) * c->cfg.num_pages; }
+int pd_cache_config_of(const pd_cache* c, pd_cache_config* out) { *out = c->cfg; return PD_OK; }
+int pd_cache_block_table(const pd_cache* c, int slot, int* out, int cap) {
+    const auto& t = c->tables[slot];
+    for (int i = 0; i < cap && i < static_cast<int>(t.size()); i++) out[i] = t[i];
+    return static_cast<int>(t.size());
+}
+int pd_cache_free_list(const pd_cache* c, int* out, int cap) {
+    for (int i = 0; i < cap && i < static_cast<int>(c->free_pages.size()); i++) out[i] = c->free_pages[i];
+    return static_cast<int>(c->free_pages.size());
+}
+
+}  // extern "C"

@@ -1,0 +1,282 @@
+"""Python mirror of the reference's `decode::` interface over the C ABI.
+
+Same names, argument meaning and error behaviour as src/decode/decode.hpp and
+src/decode/paged_kv_cache.hpp of the reference; every call goes straight into
+libpd_b200.so.  Device buffers are passed as integers (device pointers) or as
+any object with a `data_ptr()` method (torch tensors); streams as an integer
+cudaStream_t handle (0 = default stream).
+"""
+import ctypes as C
+import enum
+
+import numpy as np
+
+from . import _lib
+from ._lib import InvalidArgument, LengthError, check, pd_cache_config, pd_params
+
+DecodeParams = pd_params
+
+
+class KVDtype(enum.IntEnum):
+    """decode::KVDtype (src/decode/decode_types.hpp:8)."""
+    FP16 = 0
+    FP8_E4M3 = 1
+
+
+def kv_dtype_bytes(t):
+    return _lib.lib().pd_kv_dtype_bytes(int(t))
+
+
+def kv_dtype_name(t):
+    return _lib.lib().pd_kv_dtype_name(int(t)).decode()
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    return int(x)
+
+
+def _out_int(fn, *args):
+    v = C.c_int()
+    check(fn(*args, C.byref(v)))
+    return v.value
+
+
+def tile_tokens(dtype, head_dim, group):
+    """decode::tile_tokens (src/decode/decode.hpp:30)."""
+    return _out_int(_lib.lib().pd_tile_tokens, int(dtype), head_dim, group)
+
+
+def wave_ctas(dtype, head_dim, group):
+    """decode::wave_ctas (src/decode/decode.hpp:33)."""
+    return _out_int(_lib.lib().pd_wave_ctas, int(dtype), head_dim, group)
+
+
+def default_ctas(dtype, head_dim, group):
+    """decode::default_ctas (src/decode/decode.hpp:35)."""
+    return _out_int(_lib.lib().pd_default_ctas, int(dtype), head_dim, group)
+
+
+def set_kernel_variant(v):
+    check(_lib.lib().pd_set_kernel_variant(v))
+
+
+def kernel_variant():
+    return _lib.lib().pd_kernel_variant()
+
+
+class DecodePlan:
+    """decode::DecodePlan (src/decode/decode.hpp:21-27). Owns (or borrows) a pd_plan handle."""
+
+    def __init__(self, handle, owned=True):
+        self._h = handle
+        self._owned = owned
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._h:
+            _lib.lib().pd_plan_free(self._h)
+            self._h = None
+
+    @property
+    def num_ctas(self):
+        return _lib.lib().pd_plan_num_ctas(self._h)
+
+    @property
+    def tile(self):
+        return _lib.lib().pd_plan_tile(self._h)
+
+    @property
+    def num_segments(self):
+        return _lib.lib().pd_plan_num_segments(self._h)
+
+    @property
+    def segments(self):
+        n = self.num_segments
+        if n == 0:
+            return np.zeros((0, 4), np.int32)
+        return np.ctypeslib.as_array(_lib.lib().pd_plan_segments(self._h), shape=(n, 4)).copy()
+
+    @property
+    def cta_seg_begin(self):
+        return np.ctypeslib.as_array(_lib.lib().pd_plan_cta_seg_begin(self._h), shape=(self.num_ctas + 1,)).copy()
+
+    @property
+    def item_seg_begin(self):
+        n = _lib.lib().pd_plan_num_items(self._h)
+        return np.ctypeslib.as_array(_lib.lib().pd_plan_item_seg_begin(self._h), shape=(n + 1,)).copy()
+
+
+def _lens_arg(seq_lens):
+    lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    return lens, lens.ctypes.data_as(C.POINTER(C.c_int))
+
+
+def make_plan(dtype, seq_lens, num_q_heads, num_kv_heads, head_dim, num_ctas=0):
+    """decode::make_plan (src/decode/decode.hpp:38-39)."""
+    lens, p = _lens_arg(seq_lens)
+    h = C.c_void_p()
+    check(_lib.lib().pd_make_plan(int(dtype), p, len(lens), num_q_heads, num_kv_heads, head_dim, num_ctas, C.byref(h)))
+    return DecodePlan(h)
+
+
+def make_plan_tiled(tile, seq_lens, num_q_heads, num_kv_heads, num_ctas):
+    """The planner with an explicit tile size; host arithmetic only."""
+    lens, p = _lens_arg(seq_lens)
+    h = C.c_void_p()
+    check(_lib.lib().pd_make_plan_tiled(tile, p, len(lens), num_q_heads, num_kv_heads, num_ctas, C.byref(h)))
+    return DecodePlan(h)
+
+
+class DevicePlan:
+    """decode::DevicePlan (src/decode/decode.hpp:44-62)."""
+
+    def __init__(self):
+        h = C.c_void_p()
+        check(_lib.lib().pd_device_plan_create(C.byref(h)))
+        self._h = h
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _lib.lib().pd_device_plan_destroy(self._h)
+            self._h = None
+
+    def upload(self, plan, group, head_dim, stream=0):
+        check(_lib.lib().pd_device_plan_upload(self._h, plan._h, group, head_dim, stream))
+
+    def bind(self, params):
+        check(_lib.lib().pd_device_plan_bind(self._h, C.byref(params)))
+
+
+def paged_decode(dtype, params, stream=0, num_pages=0):
+    """decode::paged_decode (src/decode/decode.hpp:66)."""
+    check(_lib.lib().pd_paged_decode_bounded(int(dtype), C.byref(params), num_pages, stream))
+
+
+def kernel_status(stream=0):
+    """Raises KernelTimeout if a bounded device-side wait of an earlier decode expired."""
+    st = C.c_uint()
+    check(_lib.lib().pd_kernel_status(stream, C.byref(st)))
+    return st.value
+
+
+def append_tokens(dtype, d_k, d_v, k_cache, v_cache, d_block_table_row, start_pos, n, num_kv_heads, head_dim,
+                  page_size, k_scale=1.0, v_scale=1.0, stream=0):
+    """append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers."""
+    check(_lib.lib().pd_append_tokens(int(dtype), _ptr(d_k), _ptr(d_v), _ptr(k_cache), _ptr(v_cache),
+                                      _ptr(d_block_table_row), start_pos, n, num_kv_heads, head_dim, page_size,
+                                      k_scale, v_scale, stream))
+
+
+class PagedKVCache:
+    """decode::PagedKVCache (src/decode/paged_kv_cache.hpp:17-93)."""
+
+    class Config:
+        def __init__(self, num_pages=0, page_size=0, num_kv_heads=0, head_dim=0, max_slots=0, max_pages_per_slot=0,
+                     dtype=KVDtype.FP16, k_scale=1.0, v_scale=1.0):
+            self.num_pages, self.page_size, self.num_kv_heads, self.head_dim = num_pages, page_size, num_kv_heads, head_dim
+            self.max_slots, self.max_pages_per_slot = max_slots, max_pages_per_slot
+            self.dtype, self.k_scale, self.v_scale = dtype, k_scale, v_scale
+
+        def _c(self):
+            return pd_cache_config(self.num_pages, self.page_size, self.num_kv_heads, self.head_dim, self.max_slots,
+                                   self.max_pages_per_slot, int(self.dtype), self.k_scale, self.v_scale)
+
+    def __init__(self, cfg):
+        self._h = None
+        self._cfg = cfg
+        h = C.c_void_p()
+        c = cfg._c()
+        check(_lib.lib().pd_cache_create(C.byref(c), C.byref(h)))
+        self._h = h
+
+    def close(self):
+        if self._h:
+            _lib.lib().pd_cache_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    @staticmethod
+    def bytes_per_page(cfg):
+        c = cfg._c()
+        return _lib.lib().pd_cache_bytes_per_page(C.byref(c))
+
+    @staticmethod
+    def pages_for_budget(cfg, budget_bytes):
+        c = cfg._c()
+        return _lib.lib().pd_cache_pages_for_budget(C.byref(c), budget_bytes)
+
+    def admit(self):
+        return _lib.lib().pd_cache_admit(self._h)
+
+    def append(self, slot, d_k, d_v, n, stream=0):
+        """True when appended, False (nothing changed) when the pool is out of pages."""
+        rc = _lib.lib().pd_cache_append(self._h, slot, _ptr(d_k), _ptr(d_v), n, stream)
+        if rc == _lib.PD_OUT_OF_PAGES:
+            return False
+        check(rc)
+        return True
+
+    def release(self, slot):
+        check(_lib.lib().pd_cache_release(self._h, slot))
+
+    def shuffle_free_pages(self, seed):
+        _lib.lib().pd_cache_shuffle_free_pages(self._h, seed)
+
+    def plan(self, slots, num_q_heads, num_ctas=0, stream=0):
+        s = np.ascontiguousarray(slots, dtype=np.int32)
+        check(_lib.lib().pd_cache_plan(self._h, s.ctypes.data_as(C.POINTER(C.c_int)), len(s), num_q_heads, num_ctas, stream))
+
+    def run(self, d_q, d_out, stream=0):
+        check(_lib.lib().pd_cache_run(self._h, _ptr(d_q), _ptr(d_out), stream))
+
+    def decode(self, d_q, d_out, batch, num_q_heads, num_ctas=0, stream=0):
+        check(_lib.lib().pd_cache_decode(self._h, _ptr(d_q), _ptr(d_out), batch, num_q_heads, num_ctas, stream))
+
+    def last_plan(self):
+        h = _lib.lib().pd_cache_last_plan(self._h)
+        return DecodePlan(C.c_void_p(h), owned=False) if h else None
+
+    def params(self):
+        p = pd_params()
+        check(_lib.lib().pd_cache_params(self._h, C.byref(p)))
+        return p
+
+    def seq_len(self, slot):
+        return _lib.lib().pd_cache_seq_len(self._h, slot)
+
+    def occupied(self, slot):
+        return bool(_lib.lib().pd_cache_occupied(self._h, slot))
+
+    def free_pages(self):
+        return _lib.lib().pd_cache_free_pages(self._h)
+
+    def max_seq_len(self):
+        return _lib.lib().pd_cache_max_seq_len(self._h)
+
+    def total_bytes(self):
+        return _lib.lib().pd_cache_total_bytes(self._h)
+
+    def config(self):
+        return self._cfg
+
+    def block_table(self, slot):
+        cap = self._cfg.max_pages_per_slot
+        out = np.zeros(cap, np.int32)
+        n = _lib.lib().pd_cache_block_table(self._h, slot, out.ctypes.data_as(C.POINTER(C.c_int)), cap)
+        return out[:n].copy()
+
+    def free_list(self):
+        cap = self._cfg.num_pages
+        out = np.zeros(cap, np.int32)
+        n = _lib.lib().pd_cache_free_list(self._h, out.ctypes.data_as(C.POINTER(C.c_int)), cap)
+        return out[:n].copy()
+
+
+__all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
+           "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
+           "make_plan_tiled", "paged_decode", "append_tokens", "kernel_status", "set_kernel_variant", "kernel_variant"]
