@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the paged split-KV decode layer (one step = one decode layer over one batch).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5|small|...]
+
+Prints ONE JSON line.  Metric: achieved HBM GB/s over the algorithmic bytes of the
+layer (K+V of every token once, q and out, block-table entries), with the layer
+time in `ms_per_step`.  Inputs are synthetic, seeded, N(0,1), of the shape the
+workload names; pages are scattered through a pool sized exactly to fit.
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): by default the batch
+is sharded, every rank holds its own full-size layer shard (weak scaling) and the
+outputs are all-gathered over NCCL inside the timed step; `--shard heads` splits
+the KV heads of one fixed problem instead (strong scaling, workload c5).
+
+`--impl reference` times the reference's own CPU attention (compiled from its
+sources into oracle/_ref, else the oracle port) on a bounded sample of the same
+workload, on the host cores of this box.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (dtype, batch, seq_len, hq, hkv, page, description)
+    "c2": (0, 64, 8192, 32, 8, 16, "Llama-3-8B layer, batch 64 x 8192, fp16 KV, 16-token pages scattered"),
+    "c3": (1, 128, 4096, 32, 8, 16, "Llama-3-8B layer, batch 128 x 4096, fp8 e4m3 KV, 16-token pages scattered"),
+    "c5": (1, 256, 16384, 64, 8, 16, "Llama-3-70B-shaped layer, batch 256 x 16384, fp8 e4m3 KV, kv heads sharded"),
+    "c2-onepage": (0, 64, 8192, 32, 8, 8192, "c2 with one contiguous 8192-token page per sequence"),
+    "small": (0, 8, 8192, 32, 8, 16, "profiling case: batch 8 x 8192 fp16 (268 MB of KV, larger than L2)"),
+    "small-fp8": (1, 16, 8192, 32, 8, 16, "profiling case: batch 16 x 8192 fp8 (268 MB of KV)"),
+}
+
+
+def algorithmic_bytes(dtype, lens, hq, hkv, page, d=128):
+    """bytes = 2*sum(len)*Hkv*d*elem + 2*B*Hq*d*2 + 4*sum(ceil(len/page)) (bench/bench_decode.cu:186-191 of the reference)."""
+    elem = 2 if dtype == 0 else 1
+    return (2 * sum(lens) * hkv * d * elem + 2 * len(lens) * hq * d * 2
+            + 4 * sum((n + page - 1) // page for n in lens))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.lines = []
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's cpu_attention over a bounded sample
+# ---------------------------------------------------------------------------------------------
+
+def cpu_sample_inputs(dtype, rows, L, hq, hkv, page, seed=7):
+    """Host-side paged cache for `rows` sequences of length L, N(0,1) fp16 values, scattered pages."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    rng = np.random.default_rng(seed)
+    pages = (L + page - 1) // page
+    perm = rng.permutation(rows * pages).astype(np.int32).reshape(rows, pages)
+    scale = 5.0 / 448.0 if dtype == 1 else 1.0
+    np_dt = np.uint16 if dtype == 0 else np.uint8
+    kc = np.zeros(rows * pages * hkv * page * 128, np_dt)
+    vc = np.zeros_like(kc)
+    for r in range(rows):
+        k = rng.standard_normal((L, hkv, 128), dtype=np.float32).astype(np.float16)
+        v = rng.standard_normal((L, hkv, 128), dtype=np.float32).astype(np.float16)
+        ol.append(dtype, k.view(np.uint16), v.view(np.uint16), kc, vc, perm[r], 0, hkv, 128, page, scale, scale)
+    q = rng.standard_normal((rows, hq, 128), dtype=np.float32).astype(np.float16)
+    return q, kc, vc, perm, scale
+
+
+def run_cpu_attention(dtype, q, kc, vc, bt, lens, hq, hkv, page, scale, threads):
+    """Returns (seconds of attention calls, kind, out) using oracle/_ref when present, else the oracle port."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    rows = q.shape[0]
+    out = np.zeros((rows, hq, 128), np.float32)
+    lens_a = np.ascontiguousarray(lens, np.int32)
+    bt = np.ascontiguousarray(bt, np.int32)
+    R = ol.ref()
+    i32p, u16p, f32p = C.POINTER(C.c_int), C.POINTER(C.c_uint16), C.POINTER(C.c_float)
+    if R is not None:
+        rws = np.arange(rows, dtype=np.int32)
+        secs = C.c_double()
+        R.ref_paged_cpu_decode(dtype, q.view(np.uint16).ctypes.data_as(u16p), kc.ctypes.data, vc.ctypes.data,
+                               bt.ctypes.data_as(i32p), bt.shape[1], lens_a.ctypes.data_as(i32p),
+                               rws.ctypes.data_as(i32p), rows, hq, hkv, 128, page, C.c_float(scale), C.c_float(scale),
+                               out.ctypes.data_as(f32p), threads, C.byref(secs))
+        return secs.value, "reference", out
+    t0 = time.perf_counter()
+    out = ol.paged_decode(0, dtype, q.view(np.uint16), kc, vc, bt, lens_a, hq, hkv, 128, page, k_scale=scale,
+                          v_scale=scale, threads=threads)
+    return time.perf_counter() - t0, "port", out
+
+
+def cpu_leg(dtype, L, hq, hkv, page, batch, target_seconds=10.0):
+    """Times the CPU attention on a bounded sample: calibrates on one row, then sizes the sample."""
+    cores = os.cpu_count() or 1
+    q, kc, vc, bt, scale = cpu_sample_inputs(dtype, 1, L, hq, hkv, page)
+    t1, kind, _ = run_cpu_attention(dtype, q, kc, vc, bt, [L], hq, hkv, page, scale, cores)
+    rows = int(max(1, min(batch, target_seconds / max(t1, 1e-6))))
+    if rows > 1:
+        q, kc, vc, bt, scale = cpu_sample_inputs(dtype, rows, L, hq, hkv, page)
+        secs, kind, _ = run_cpu_attention(dtype, q, kc, vc, bt, [L] * rows, hq, hkv, page, scale, cores)
+    else:
+        secs = t1
+    nbytes = algorithmic_bytes(dtype, [L] * rows, hq, hkv, page)
+    return {"value": nbytes / secs / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"{rows} of {batch} sequences x {hq} q heads at length {L} "
+                      f"({'cpu_attention from the reference sources' if kind == 'reference' else 'oracle port of cpu_attention'}, "
+                      f"OpenMP over (row, q head), gather excluded, {secs:.2f} s)",
+            "seconds": secs, "rows": rows}
+
+
+def reference_arm(args, wl):
+    dtype, B, L, hq, hkv, page, desc = wl
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    # calibrate the sample so that warmup + steps finish within a few minutes
+    q, kc, vc, bt, scale = cpu_sample_inputs(dtype, 1, L, hq, hkv, page)
+    t1, kind, _ = run_cpu_attention(dtype, q, kc, vc, bt, [L], hq, hkv, page, scale, cores)
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    rows = int(max(1, min(B, budget / max(t1, 1e-6))))
+    q, kc, vc, bt, scale = cpu_sample_inputs(dtype, rows, L, hq, hkv, page)
+    for _ in range(args.warmup):
+        run_cpu_attention(dtype, q, kc, vc, bt, [L] * rows, hq, hkv, page, scale, cores)
+    secs = [run_cpu_attention(dtype, q, kc, vc, bt, [L] * rows, hq, hkv, page, scale, cores)[0] for _ in range(args.steps)]
+    nbytes = algorithmic_bytes(dtype, [L] * rows, hq, hkv, page)
+    per = sum(secs) / len(secs)
+    value = nbytes / per / 1e9
+    sample = (f"each step = {rows} of {B} sequences x {hq} q heads at length {L}; "
+              f"{'cpu_attention compiled from the reference sources (oracle/_ref)' if kind == 'reference' else 'oracle port of cpu_attention'}, "
+              f"{cores} OpenMP threads, gather excluded")
+    print(json.dumps({
+        "impl": "reference", "metric": "paged_decode_achieved_hbm_bandwidth", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+
+def our_arm(args, wl):
+    import torch
+    import paged_attention_b200 as pa
+
+    dtype, B, L, hq, hkv, page, desc = wl
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the engine has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.variant is not None:
+        pa.set_kernel_variant(args.variant)
+
+    shard = args.shard or ("heads" if args.workload == "c5" else "batch")
+    if shard == "heads":
+        if hkv % world or hq % world:
+            raise SystemExit("--shard heads needs the head counts to divide by the number of GPUs")
+        l_hq, l_hkv, l_B = hq // world, hkv // world, B
+        scaling = "strong"
+    else:
+        l_hq, l_hkv, l_B = hq, hkv, B          # every rank holds a full-size shard of the global batch
+        scaling = "weak"
+    group = l_hq // l_hkv
+    lens = [L] * l_B
+    pages = (L + page - 1) // page
+    scale = 5.0 / 448.0 if dtype == 1 else 1.0
+    cfg = pa.PagedKVCache.Config(num_pages=pages * l_B, page_size=page, num_kv_heads=l_hkv, head_dim=128,
+                                 max_slots=l_B, max_pages_per_slot=pages, dtype=pa.KVDtype(dtype), k_scale=scale,
+                                 v_scale=scale)
+    cache = pa.PagedKVCache(cfg)
+    if not args.contiguous_pages:
+        cache.shuffle_free_pages(42)
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    for b in range(l_B):
+        k = torch.randn(L, l_hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
+        v = torch.randn(L, l_hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
+        slot = cache.admit()
+        if not cache.append(slot, k, v, L, stream):
+            raise SystemExit("bench.py: pool out of pages")
+    del k, v
+    q_host = torch.randn(l_B, l_hq, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(99 + rank)).pin_memory()
+    out_host = torch.empty_like(q_host).pin_memory()
+    q = q_host.cuda()
+    out = torch.zeros_like(q)
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device="cuda") if world > 1 else None
+
+    # Drive the kernel through the plan API, as a serving engine does: plan once per step, run per layer.
+    plan = pa.make_plan(pa.KVDtype(dtype), lens, l_hq, l_hkv, 128, args.ctas)
+    dplan = pa.DevicePlan()
+    dplan.upload(plan, group, 128, stream)
+    params = cache.params()
+    params.q, params.out = q.data_ptr(), out.data_ptr()
+    params.batch, params.num_q_heads = l_B, l_hq
+    dplan.bind(params)
+    needs_merge = params.needs_merge
+
+    flush_buf = torch.zeros(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def flush():   # read-only pass over 4x L2: the next kernel starts cold and L2 holds no dirty lines
+        pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)
+
+    def step():
+        pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def step_decode_only():
+        params.needs_merge = 0
+        pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
+        params.needs_merge = needs_merge
+
+    def step_e2e():
+        q.copy_(q_host, non_blocking=True)
+        step()
+        out_host.copy_(out if world == 1 else gathered[rank], non_blocking=True)
+
+    def timed(fn, steps):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in ev:
+            flush()
+            s.record()
+            fn()
+            e.record()
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) for s, e in ev]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush()
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_wall0 = time.perf_counter()
+    ms = timed(step, args.steps)
+    barrier()
+    wall = time.perf_counter() - t_wall0
+    ms_decode = timed(step_decode_only, args.steps)
+    ms_e2e = timed(step_e2e, args.steps)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    pa.kernel_status(stream)
+
+    total = torch.tensor([sum(ms), sum(ms_decode), sum(ms_e2e)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    total = total.tolist()
+    per_step, per_decode, per_e2e = (t / args.steps for t in total)
+
+    local_bytes = algorithmic_bytes(dtype, lens, l_hq, l_hkv, page)
+    job_bytes = local_bytes * world
+    value = job_bytes / (per_step * 1e-3) / 1e9
+    e2e_value = job_bytes / (per_e2e * 1e-3) / 1e9
+    peak, peak_src = measured_peak()
+    achieved = local_bytes / (per_decode * 1e-3) / 1e9
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cpu = cpu_leg(dtype, L, hq, hkv, page, B)
+            cpu.pop("seconds", None)
+            cpu.pop("rows", None)
+        line = {
+            "metric": "paged_decode_achieved_hbm_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step,
+            "us_per_layer": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "f16 mma, f32 accumulate (KV %s)" % ("fp16" if dtype == 0 else "fp8_e4m3"),
+            "data": "synthetic",
+            "config": {"workload": desc, "name": args.workload, "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
+                       "kv_heads_per_gpu": l_hkv, "page_size": page, "sharding": "none" if world == 1 else shard,
+                       "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
+                       "ctas": plan.num_ctas, "segments": plan.num_segments, "tile": plan.tile,
+                       "kernel_variant": pa.kernel_variant(),
+                       "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
+                             % (local_bytes / 1e6),
+                       "timing": "CUDA events around decode+merge%s per step, summed over steps, max over ranks"
+                                 % (" + NCCL all-gather" if world > 1 else "")},
+            "algorithmic_bytes_per_step": job_bytes,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "paged_decode_kernel",
+                         "kernel_ms": per_decode, "frac_of_8TBps_nominal": achieved / 8000.0},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": per_e2e,
+                    "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "note": "pinned q -> device, decode+merge, out -> pinned host, per step; the KV cache is resident state"},
+            "gpu_launches": args.steps * ((2 if needs_merge else 1) + 1),
+            "gpu_launches_note": "per step: paged_decode_kernel%s + stream_read_kernel (L2 flush)" % (" + merge_segments_kernel" if needs_merge else ""),
+            "clocks": clocks, "wall_s_timed_region": wall,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as f:
+                t = json.load(f).get(args.workload)
+            if t:
+                line["roofline"]["traffic"] = t["dram_bytes_per_launch"]
+                line["roofline"]["traffic_source"] = t["source"]
+        print(json.dumps(line))
+    cache.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--shard", default=None, choices=["batch", "heads"])
+    ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--variant", type=int, default=None)
+    ap.add_argument("--contiguous-pages", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, wl)
+    else:
+        our_arm(args, wl)
+
+
+if __name__ == "__main__":
+    main()

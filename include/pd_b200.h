@@ -147,6 +147,11 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
  * Nonzero encodes (code << 24 | cta) of the first wait that gave up. */
 int pd_kernel_status(void* stream, unsigned* status);
 
+/* read_kernel of the reference's benchmark (bench/bench_decode.cu:69-78, "copy" mode
+ * :224-240): a read-only streaming pass over `bytes` of device memory with `blocks`
+ * CTAs of 512 threads; the attainable HBM read rate decode is compared with. */
+int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream);
+
 /* append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers:
  * scatter n tokens of fp16 K/V ([n][num_kv_heads][head_dim], device) into the
  * pools through one slot's block-table row (device), quantising to E4M3 with

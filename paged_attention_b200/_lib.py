@@ -80,6 +80,7 @@ SIGNATURES = {
     "pd_paged_decode": (C.c_int, [C.c_int, C.POINTER(pd_params), _vp]),
     "pd_paged_decode_bounded": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp]),
     "pd_kernel_status": (C.c_int, [_vp, C.POINTER(C.c_uint)]),
+    "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
     "pd_append_tokens": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_float, C.c_float, _vp]),
     "pd_cache_bytes_per_page": (C.c_size_t, [C.POINTER(pd_cache_config)]),

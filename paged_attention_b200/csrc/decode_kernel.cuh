@@ -39,6 +39,10 @@ constexpr int HEAD_DIM = 128;
 constexpr int OSTRIDE  = HEAD_DIM + 4;   // padded row of the cross-warp merge scratch (floats)
 
 // status word codes (code << 24 | blockIdx)
+// diagnostic flags carried above the box-size bits of the kernel's btl_flags argument
+constexpr int FLAG_LOAD_ONLY = 0x100;
+constexpr int FLAG_NO_L2_HINT = 0x200;
+
 constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a tile
 constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
 constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
@@ -123,6 +127,18 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
                  " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(pol) : "memory");
 }
+__device__ __forceinline__ void tma_load_4d_nohint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                   int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_nohint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                   int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -180,9 +196,11 @@ __device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
 template<typename KV, int GROUP, typename C>
 __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const int btl /* log2(box tokens) */,
+                    const __grid_constant__ CUtensorMap v_map, const int btl_flags /* log2(box tokens) | diagnostic flags */,
                     unsigned* __restrict__ status)
 {
+    const int  btl     = btl_flags & 0xff;
+    const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
     using S = Shape<KV, GROUP, C>;
     constexpr bool FP8 = sizeof(KV) == 1;
     constexpr int STAGES = C::STAGES;
@@ -251,7 +269,15 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const uint32_t v_dst = k_dst + S::TILE_BYTES;
             auto copy_box = [&](int j, int page) {
                 const int tok_in_page = (tile_tok + (j << btl)) % ps;
-                if constexpr (FP8) {
+                if (btl_flags & FLAG_NO_L2_HINT) {
+                    if constexpr (FP8) {
+                        tma_load_4d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, sg.y, page);
+                        tma_load_4d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, sg.y, page);
+                    } else {
+                        tma_load_5d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page);
+                        tma_load_5d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page);
+                    }
+                } else if constexpr (FP8) {
                     tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
                     tma_load_4d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
                 } else {
@@ -371,7 +397,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 #pragma unroll
             for (int gi = 0; gi < C::GROUPS_PER_WARP; gi++) {
                 const int grp_row = (warp * C::GROUPS_PER_WARP + gi) * 16;
-                if (grp_row >= valid) break;                      // warp-uniform
+                if (grp_row >= valid || no_math) break;           // warp-uniform
                 const int grp_valid = valid - grp_row;            // >= 1; < 16 only in a sequence's last group
 
                 if (grp_valid < 16) {

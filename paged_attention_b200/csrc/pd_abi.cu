@@ -8,6 +8,7 @@
 
 #include "append_kernel.cuh"
 #include "decode_kernel.cuh"
+#include "probe_kernel.cuh"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -208,6 +209,11 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
         return set_error(PD_INVALID_ARGUMENT, "KV pool pointer must be 16-byte aligned");
     const cuuint64_t pages = num_pages > 0 ? static_cast<cuuint64_t>(num_pages) : (1ull << 31);
     const cuuint64_t row = dtype == PD_FP16 ? 256 : 128;
+    static const int promo_env = std::getenv("PD_B200_L2PROMO") ? std::atoi(std::getenv("PD_B200_L2PROMO")) : 3;
+    const CUtensorMapL2promotion promo = promo_env == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                       : promo_env == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                       : promo_env == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                        : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     CUresult r;
     if (dtype == PD_FP16) {
         const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
@@ -215,7 +221,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
         const cuuint32_t box[5]     = {64, 1u << btl, 2, 1, 1};
         const cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
         r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(pool), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         const cuuint64_t dims[4]    = {128, static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(num_kv_heads), pages};
@@ -223,7 +229,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
         const cuuint32_t box[4]     = {128, 1u << btl, 1, 1};
         const cuuint32_t estr[4]    = {1, 1, 1, 1};
         r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(pool), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) return set_error(PD_CUDA_ERROR, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
@@ -550,7 +556,9 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(*p, k_map, v_map, btl, status, stream);
+    static const bool load_only = std::getenv("PD_B200_LOAD_ONLY") != nullptr;   // diagnostic, see decode_kernel.cuh
+    static const bool no_hint = std::getenv("PD_B200_NO_L2_HINT") != nullptr;
+    k->launch(*p, k_map, v_map, btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0), status, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge) {
         k->merge(*p, stream);
@@ -573,6 +581,19 @@ int pd_kernel_status(void* stream, unsigned* out) {
         PD_CUDA(cudaMemset(status, 0, sizeof(unsigned)));
         return set_error(PD_KERNEL_TIMEOUT, "decode kernel: bounded wait %u expired in CTA %u", *out >> 24, *out & 0xffffffu);
     }
+    return PD_OK;
+}
+
+// ---- bandwidth probe ---------------------------------------------------------------------------------------
+
+int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream_) {
+    if (!d_buf || bytes < 16 || blocks <= 0 || reinterpret_cast<uintptr_t>(d_buf) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "stream_read: bad argument");
+    unsigned* sink = nullptr;
+    if (int rc = status_word(&sink)) return rc;   // never written: the fold value cannot match
+    pdk::stream_read_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const uint4*>(d_buf), bytes / 16, sink);
+    PD_CUDA(cudaGetLastError());
     return PD_OK;
 }
 

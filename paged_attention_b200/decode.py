@@ -162,6 +162,11 @@ def kernel_status(stream=0):
     return st.value
 
 
+def stream_read(d_buf, nbytes, blocks, stream=0):
+    """Read-only streaming pass (the reference benchmark's "copy" probe)."""
+    check(_lib.lib().pd_stream_read(_ptr(d_buf), nbytes, blocks, stream))
+
+
 def append_tokens(dtype, d_k, d_v, k_cache, v_cache, d_block_table_row, start_pos, n, num_kv_heads, head_dim,
                   page_size, k_scale=1.0, v_scale=1.0, stream=0):
     """append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers."""
@@ -279,4 +284,4 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "paged_decode", "append_tokens", "kernel_status", "set_kernel_variant", "kernel_variant"]
+           "make_plan_tiled", "paged_decode", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant"]

@@ -137,3 +137,34 @@ def run_case(case, torch, pa, check_bytes=True, precision=1):
     info = dict(num_ctas=plan.num_ctas, segments=plan.num_segments)
     cache.close()
     return err, out, want, info
+
+
+def raw_decode(torch, pa, dtype, dq, k_cache, v_cache, block_table, seq_lens, hq, hkv, ps, k_scale=1.0, v_scale=1.0,
+               num_ctas=0, slot_ids=None, num_pages=0, d=128):
+    """Drives the kernel directly on caller-owned buffers, as the reference's torch binding does
+    (bindings/torch_decode.cu:21-59): plan from host lengths, upload, fill DecodeParams by hand, decode.
+    k_cache / v_cache / dq are torch CUDA tensors; block_table a numpy int32 matrix. Returns the output tensor."""
+    B = dq.shape[0]
+    lens = np.ascontiguousarray(seq_lens, np.int32)
+    rows = lens if slot_ids is None else lens[np.asarray(slot_ids)]
+    plan = pa.make_plan(pa.KVDtype(dtype), rows, hq, hkv, d, num_ctas)
+    dp = pa.DevicePlan()
+    dp.upload(plan, hq // hkv, d)
+    d_bt = torch.from_numpy(np.ascontiguousarray(block_table, np.int32)).cuda()
+    d_lens = torch.from_numpy(lens).cuda()
+    d_slots = torch.from_numpy(np.ascontiguousarray(slot_ids, np.int32)).cuda() if slot_ids is not None else None
+    out = torch.zeros_like(dq)
+    p = pa.DecodeParams()
+    p.q, p.out = dq.data_ptr(), out.data_ptr()
+    p.k_cache, p.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    p.block_table, p.seq_lens = d_bt.data_ptr(), d_lens.data_ptr()
+    p.slot_ids = d_slots.data_ptr() if d_slots is not None else None
+    p.block_table_stride = d_bt.shape[1]
+    p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim, p.page_size = B, hq, hkv, d, ps
+    p.sm_scale = 1.0 / float(np.sqrt(np.float32(d)))
+    p.k_scale, p.v_scale = k_scale, v_scale
+    dp.bind(p)
+    pa.paged_decode(pa.KVDtype(dtype), p, 0, num_pages)
+    torch.cuda.synchronize()
+    assert pa.kernel_status() == 0
+    return out, plan
