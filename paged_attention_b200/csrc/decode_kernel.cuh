@@ -201,6 +201,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 {
     const int  btl     = btl_flags & 0xff;
     const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
+    // diagnostic: use fewer pipeline stages than were allocated (bits 12..15, 0 = all)
+    const int  nst     = ((btl_flags >> 12) & 0xf) ? min(C::STAGES, (btl_flags >> 12) & 0xf) : C::STAGES;
     using S = Shape<KV, GROUP, C>;
     constexpr bool FP8 = sizeof(KV) == 1;
     constexpr int STAGES = C::STAGES;
@@ -247,7 +249,9 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         const uint32_t box_bytes = static_cast<uint32_t>(bt_tokens) * S::ROW_BYTES;
         const uint64_t pol = l2_evict_first_policy();
         const int ps = p.page_size;
-        int issued = 0;                                 // tiles issued so far (stage = issued % STAGES)
+        int issued = 0;                                 // tiles issued so far
+        int p_stage = 0;                                // stage of the next tile and the parity of its round
+        uint32_t p_phase = 0;
         bool ok = true;
 
         auto table_of = [&](int b) {
@@ -257,9 +261,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         // Issue the copies of one tile: lanes [lane0, lane0 + nb) own one box each when
         // the tile has <= 32 boxes, otherwise every lane walks boxes lane, lane+32, ...
         auto issue_tile = [&](const int4& sg, int tile_tok, int my_page, int lane0, const int* bt) -> bool {
-            const int stage = issued % STAGES;
-            const uint32_t par = ((issued / STAGES) & 1) ^ 1;
-            if (!mbar_wait(empty_bar(stage), par)) { if (lane == 0) fail(ST_EMPTY_TIMEOUT); return false; }
+            const int stage = p_stage;
+            if (!mbar_wait(empty_bar(stage), p_phase ^ 1)) { if (lane == 0) fail(ST_EMPTY_TIMEOUT); return false; }
             if (*abort_flag) return false;
             const int valid = min(S::TILE, sg.w - tile_tok);
             const int nb = (valid + bt_tokens - 1) >> btl;
@@ -293,6 +296,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                     copy_box(j, __ldg(bt + (tile_tok + (j << btl)) / ps));
             }
             issued++;
+            if (++p_stage == nst) { p_stage = 0; p_phase ^= 1; }
             return true;
         };
 
@@ -328,8 +332,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         }
         if (!ok || *abort_flag) {
             // Drain: no copy may still be in flight towards this CTA's shared memory at exit.
-            for (int i = max(0, issued - STAGES); i < issued; i++)
-                if (!mbar_wait(full_bar(i % STAGES), (i / STAGES) & 1)) { if (lane == 0) fail(ST_DRAIN_TIMEOUT); break; }
+            for (int i = 0; i < min(issued, nst); i++) {
+                int s = p_stage - 1 - i;                 // walk back over the most recent issues
+                uint32_t par = p_phase;
+                if (s < 0) { s += nst; par ^= 1; }
+                if (!mbar_wait(full_bar(s), par)) { if (lane == 0) fail(ST_DRAIN_TIMEOUT); break; }
+            }
         }
         return;
     }
@@ -343,7 +351,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     float m_run[2], l_run[2];
     uint32_t qb[8][2];          // Q^T B-fragments for the 8 k-steps
 
-    int consumed = 0;
+    int c_stage = 0;            // stage of the next tile to consume and the parity of its round
+    uint32_t c_phase = 0;
     bool alive = true;
     uint32_t sync_phase = 0;
     // All consumer warps meet here; gives up (and aborts the CTA) instead of hanging
@@ -386,8 +395,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         l_run[0] = l_run[1] = 0.f;
 
         for (int tok = sg.z; tok < sg.w; tok += S::TILE) {
-            const int stage = consumed % STAGES;
-            if (!mbar_wait(full_bar(stage), (consumed / STAGES) & 1)) { if (lane == 0) fail(ST_FULL_TIMEOUT); alive = false; break; }
+            const int stage = c_stage;
+            if (!mbar_wait(full_bar(stage), c_phase)) { if (lane == 0) fail(ST_FULL_TIMEOUT); alive = false; break; }
             if (*abort_flag) { alive = false; break; }
             const uint32_t k_tile = pipe + stage * S::STAGE_BYTES;
             const uint32_t v_tile = k_tile + S::TILE_BYTES;
@@ -520,7 +529,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             if (wrote) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(stage));
-            consumed++;
+            if (++c_stage == nst) { c_stage = 0; c_phase ^= 1; }
         }
         if (!alive) break;
 

@@ -52,22 +52,26 @@ int set_error(int code, const char* fmt, ...) {
 // ---- kernel variants ------------------------------------------------------------------
 // A variant fixes the CTA shape and pipeline depth for both cache dtypes.  Variant 0
 // is the default; the others exist for tuning runs (pd_set_kernel_variant).
-
 template<int V, typename KV> struct VariantConfig;
-// 4 consumer warps, 64-token tiles, 96 KB of pipeline, two CTAs per SM.
+// Default.  4 consumer warps + 1 producer warp per CTA, 64-token tiles.  fp16: 3 stages of
+// 32 KB, two CTAs per SM; fp8: 3 stages of 16 KB, three CTAs per SM (the fp8 widening is a
+// long dependent chain, so it wants more warps).  Both keep about 96..128 KB of copies in
+// flight per SM, where the measured load rate of the pipeline peaks; more in flight is slower.
 template<> struct VariantConfig<0, __half>        { using type = pdk::Config<4, 1, 3, 2>; };
-template<> struct VariantConfig<0, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 6, 2>; };
-// 8 consumer warps, 128-token tiles, 192 KB of pipeline, one CTA per SM.
+template<> struct VariantConfig<0, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 3, 3>; };
+// 8 consumer warps, 128-token tiles, one CTA per SM.
 template<> struct VariantConfig<1, __half>        { using type = pdk::Config<8, 1, 3, 1>; };
 template<> struct VariantConfig<1, __nv_fp8_e4m3> { using type = pdk::Config<8, 1, 6, 1>; };
 // 4 consumer warps, 64-token tiles, deep pipeline, one CTA per SM.
 template<> struct VariantConfig<2, __half>        { using type = pdk::Config<4, 1, 6, 1>; };
 template<> struct VariantConfig<2, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 12, 1>; };
-// 8 consumer warps on 64-token tiles is not expressible (one group per warp), so
-// variant 3 gives each of 4 warps two groups: 128-token tiles, one CTA per SM.
+// 4 consumer warps with two 16-token groups each: 128-token tiles, one CTA per SM.
 template<> struct VariantConfig<3, __half>        { using type = pdk::Config<4, 2, 3, 1>; };
 template<> struct VariantConfig<3, __nv_fp8_e4m3> { using type = pdk::Config<4, 2, 6, 1>; };
-constexpr int NUM_VARIANTS = 4;
+// Three CTAs per SM for fp16 as well; fp8 with two CTAs per SM and a deeper pipeline.
+template<> struct VariantConfig<4, __half>        { using type = pdk::Config<4, 1, 2, 3>; };
+template<> struct VariantConfig<4, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 6, 2>; };
+constexpr int NUM_VARIANTS = 5;
 
 struct KernelInfo {
     const void* fn;
@@ -116,6 +120,7 @@ const KernelInfo* info_by_variant(int variant, int group) {
         case 1: return info_by_group<KV, 1>(group);
         case 2: return info_by_group<KV, 2>(group);
         case 3: return info_by_group<KV, 3>(group);
+        case 4: return info_by_group<KV, 4>(group);
     }
     return nullptr;
 }
@@ -558,7 +563,10 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     static const bool load_only = std::getenv("PD_B200_LOAD_ONLY") != nullptr;   // diagnostic, see decode_kernel.cuh
     static const bool no_hint = std::getenv("PD_B200_NO_L2_HINT") != nullptr;
-    k->launch(*p, k_map, v_map, btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0), status, stream);
+    static const int stage_limit = std::getenv("PD_B200_STAGE_LIMIT") ? (std::atoi(std::getenv("PD_B200_STAGE_LIMIT")) & 0xf) : 0;
+    k->launch(*p, k_map, v_map,
+              btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
+              status, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge) {
         k->merge(*p, stream);
@@ -585,6 +593,17 @@ int pd_kernel_status(void* stream, unsigned* out) {
 }
 
 // ---- bandwidth probe ---------------------------------------------------------------------------------------
+
+int pd_stream_read_pattern(const void* d_buf, size_t bytes, int blocks, int pattern, void* stream_) {
+    if (!d_buf || bytes < 16 || blocks <= 0 || reinterpret_cast<uintptr_t>(d_buf) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "stream_read: bad argument");
+    unsigned* sink = nullptr;
+    if (int rc = status_word(&sink)) return rc;
+    pdk::stream_read_pattern_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream_)>>>(
+        static_cast<const uint4*>(d_buf), bytes / 16, pattern, sink);
+    PD_CUDA(cudaGetLastError());
+    return PD_OK;
+}
 
 int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream_) {
     if (!d_buf || bytes < 16 || blocks <= 0 || reinterpret_cast<uintptr_t>(d_buf) % 16 != 0)

@@ -238,7 +238,7 @@ def test_fp8_cache_against_fp16_cache(torch_cuda, pa):
     assert 1e-3 < rel < 6e-2
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 @pytest.mark.parametrize("dtype", [FP16, FP8])
 def test_kernel_variants(variant, dtype, torch_cuda, pa):
     v0 = pa.kernel_variant()
