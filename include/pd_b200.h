@@ -142,6 +142,29 @@ int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
 int pd_paged_decode(int dtype, const pd_params* p, void* stream);
 int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream);
 
+/* No counterpart in the reference (its DevicePlan always allocates, src/decode/decode.cu:131-141).
+ * The same decode + merge as pd_paged_decode_bounded, for callers that cannot allow a device
+ * allocation: a server that has already given all free HBM to its KV pool, so that a workspace
+ * cudaMalloc at step time would fail, or a step loop that forbids cudaMalloc/cudaFree because
+ * they stall the whole device.  This call, including its first use, performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ *   - p->partial_out / p->partial_lse are ignored: the workspace for rows split across CTAs is
+ *     an 8 MiB array built into the library (each GPU that loads the library carries it until
+ *     the process exits).  num_segments is the plan's segment count; a plan that needs more than
+ *     8 MiB, i.e. num_segments * group * (head_dim + 1) * 4 bytes, is refused with
+ *     PD_INVALID_ARGUMENT and nothing is launched.  Headline shapes need 0.4 - 1.6 MiB.
+ *   - d_status: device word the kernel writes if a bounded wait expires; the caller zeroes it and
+ *     reads it back when it wants to know.  NULL selects a built-in word that nothing reads.
+ *   - The first call on each device looks up the built-in arrays' device addresses
+ *     (cudaGetSymbolAddress) and raises the kernel's shared-memory limit; make that first call
+ *     during start-up, with the intended device current and before any stream capture begins.
+ *   - All calls on a device share the one workspace and it keeps whatever the previous call left
+ *     there.  Nothing in it has to start at zero (every slot the merge reads was written by the
+ *     decode kernel of the same call), but two calls that overlap on the GPU - different streams,
+ *     or one stream without ordering between them - overwrite each other's partials.  Order them. */
+int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int num_pages,
+                           unsigned* d_status, void* stream);
+
 /* Device status word of the last decode launched by this thread's library state:
  * 0 = every bounded wait completed.  Reads it back (synchronises `stream`).
  * Nonzero encodes (code << 24 | cta) of the first wait that gave up. */

@@ -79,6 +79,7 @@ SIGNATURES = {
     "pd_device_plan_bind": (C.c_int, [_vp, C.POINTER(pd_params)]),
     "pd_paged_decode": (C.c_int, [C.c_int, C.POINTER(pd_params), _vp]),
     "pd_paged_decode_bounded": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp]),
+    "pd_paged_decode_static": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, C.c_int, _vp, _vp]),
     "pd_kernel_status": (C.c_int, [_vp, C.POINTER(C.c_uint)]),
     "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
     "pd_append_tokens": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,

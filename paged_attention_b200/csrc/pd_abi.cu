@@ -579,6 +579,104 @@ int pd_paged_decode(int dtype, const pd_params* p, void* stream) {
     return pd_paged_decode_bounded(dtype, p, 0, stream);
 }
 
+// ---- decode without any allocation -------------------------------------------------------------------------
+//
+// For callers that must not let this library allocate device memory.  Two kinds exist in
+// practice: a serving process that gave every free byte of HBM to its KV pool when it started,
+// so a workspace cudaMalloc at step time fails (or lands wherever the pool left a hole); and a
+// latency-critical step loop that bans cudaMalloc/cudaFree outright because both stall the
+// whole device while they run.  The ordinary path sizes the split-row workspace
+// (partial_out | partial_lse) with cudaMalloc in pd_device_plan_upload and keeps its status word
+// in a small cudaMalloc'd cell; this entry point takes both from arrays that are part of the
+// loaded library image instead.
+//
+// The arrays below are ordinary device globals.  Their names are usable directly in device
+// code; in host code a name is only a handle for the runtime, never a device address, so the
+// address handed to the kernels comes from cudaGetSymbolAddress, once per device.
+
+namespace {
+
+constexpr size_t STATIC_SCRATCH_FLOATS = size_t(2) << 20;   // 8 MiB per GPU that loads the library
+
+static __device__ __align__(256) float    g_static_partials[STATIC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned g_static_status[64];   // [0] is the status word
+
+struct StaticScratch {
+    float*    partials = nullptr;
+    unsigned* status   = nullptr;
+    bool      ready    = false;
+};
+StaticScratch g_static_scratch[MAX_DEVICES];
+std::mutex    g_static_scratch_mutex;
+
+// One-time set-up for the current device: resolve the device addresses of the two arrays.
+int static_scratch(const StaticScratch** out) {
+    int dev = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) return set_error(PD_INTERNAL, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    StaticScratch& s = g_static_scratch[dev];
+    if (!s.ready) {
+        float* partials = nullptr;
+        unsigned* status = nullptr;
+        PD_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&partials), g_static_partials));
+        PD_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_static_status));
+        s.partials = partials;
+        s.status   = status;
+        s.ready    = true;
+    }
+    *out = &s;
+    return PD_OK;
+}
+
+}  // namespace
+
+int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int num_pages,
+                           unsigned* d_status, void* stream_) {
+    if (!p) return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: null params");
+    if (p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    const int group = p->num_q_heads / p->num_kv_heads;
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, p->head_dim, group, &k)) return rc;
+    if (p->page_size <= 0) return set_error(PD_INVALID_ARGUMENT, "page_size must be positive");
+    if (num_segments < 0) return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: num_segments must not be negative");
+    const size_t rows = static_cast<size_t>(num_segments) * group;
+    const size_t need = rows * (p->head_dim + 1);
+    if (need > STATIC_SCRATCH_FLOATS)
+        return set_error(PD_INVALID_ARGUMENT,
+                         "paged_decode_static: %d segments x group %d need %zu bytes of split-row workspace, "
+                         "the built-in workspace holds %zu bytes; plan with fewer CTAs or use pd_paged_decode",
+                         num_segments, group, need * sizeof(float), STATIC_SCRATCH_FLOATS * sizeof(float));
+    if (p->num_ctas <= 0 || p->batch <= 0) return PD_OK;
+    if (!p->q || !p->out || !p->k_cache || !p->v_cache || !p->block_table || !p->segments || !p->cta_seg_begin ||
+        !p->item_seg_begin)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: null device pointer");
+    if (int rc = configure(k)) return rc;
+    const StaticScratch* scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+
+    pd_params local = *p;                       // same launch, workspace redirected to the built-in array
+    local.partial_out = scratch->partials;
+    local.partial_lse = scratch->partials + rows * p->head_dim;
+
+    const unsigned box_tokens = gcd_u(static_cast<unsigned>(p->page_size), static_cast<unsigned>(k->tile));
+    int btl = 0;
+    while ((1u << (btl + 1)) <= box_tokens) btl++;
+    CUtensorMap k_map, v_map;
+    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, stream);
+    PD_CUDA(cudaGetLastError());
+    if (local.needs_merge) {
+        k->merge(local, stream);
+        PD_CUDA(cudaGetLastError());
+    }
+    return PD_OK;
+}
+
 int pd_kernel_status(void* stream, unsigned* out) {
     if (!out) return set_error(PD_INVALID_ARGUMENT, "kernel_status: null argument");
     unsigned* status = nullptr;

@@ -155,6 +155,14 @@ def paged_decode(dtype, params, stream=0, num_pages=0):
     check(_lib.lib().pd_paged_decode_bounded(int(dtype), C.byref(params), num_pages, stream))
 
 
+def paged_decode_static(dtype, params, num_segments, stream=0, num_pages=0, d_status=None):
+    """Decode + merge with the library's built-in split-row workspace instead of params.partial_out /
+    partial_lse: no device allocation happens in this call (there is no counterpart in the reference).
+    For callers whose process has no HBM left to allocate from, or whose step loop forbids
+    cudaMalloc/cudaFree.  Raises InvalidArgument when the plan needs more than the built-in 8 MiB."""
+    check(_lib.lib().pd_paged_decode_static(int(dtype), C.byref(params), num_segments, num_pages, _ptr(d_status), stream))
+
+
 def kernel_status(stream=0):
     """Raises KernelTimeout if a bounded device-side wait of an earlier decode expired."""
     st = C.c_uint()
@@ -284,4 +292,4 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "paged_decode", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant"]
+           "make_plan_tiled", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant"]
