@@ -118,6 +118,13 @@ int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int
  * reference's published (ctas, segments) pairs, which were made at tile 64. */
 int pd_make_plan_tiled(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
                        int num_ctas, pd_plan** out);
+/* A plan object from arrays the caller already holds: a decode::DecodePlan filled in by
+ * the caller (src/decode/decode.hpp:21-27 is a plain struct that callers may build or edit
+ * themselves before DevicePlan::upload).  The tables are checked for consistency
+ * (monotone, covering the segments, token ranges non-empty and tile-aligned);
+ * PD_INVALID_ARGUMENT otherwise.  segments holds 4 ints per segment. */
+int pd_plan_from_arrays(int num_ctas, int tile, const int* segments, int num_segments, const int* cta_seg_begin,
+                        const int* item_seg_begin, int num_items, pd_plan** out);
 void       pd_plan_free(pd_plan* plan);
 int        pd_plan_num_ctas(const pd_plan* plan);
 int        pd_plan_tile(const pd_plan* plan);

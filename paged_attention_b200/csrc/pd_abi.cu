@@ -443,6 +443,35 @@ int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int
     return build_plan(tile, seq_lens, batch, num_q_heads, num_kv_heads, num_ctas, out);
 }
 
+int pd_plan_from_arrays(int num_ctas, int tile, const int* segments, int num_segments, const int* cta_seg_begin,
+                        const int* item_seg_begin, int num_items, pd_plan** out) {
+    if (!out || num_ctas < 0 || tile <= 0 || num_segments < 0 || num_items < 0 || !cta_seg_begin || !item_seg_begin ||
+        (num_segments > 0 && !segments))
+        return set_error(PD_INVALID_ARGUMENT, "plan_from_arrays: bad argument");
+    // the tables must index the segment array consistently: the kernels trust them
+    if (cta_seg_begin[0] != 0 || cta_seg_begin[num_ctas] != num_segments || item_seg_begin[0] != 0 ||
+        item_seg_begin[num_items] != num_segments)
+        return set_error(PD_INVALID_ARGUMENT, "plan_from_arrays: tables do not cover the segments");
+    for (int c = 0; c < num_ctas; c++)
+        if (cta_seg_begin[c] > cta_seg_begin[c + 1]) return set_error(PD_INVALID_ARGUMENT, "plan_from_arrays: cta_seg_begin is not monotone");
+    for (int i = 0; i < num_items; i++)
+        if (item_seg_begin[i] > item_seg_begin[i + 1]) return set_error(PD_INVALID_ARGUMENT, "plan_from_arrays: item_seg_begin is not monotone");
+    for (int s = 0; s < num_segments; s++) {
+        const int* g = segments + 4 * s;
+        if (g[0] < 0 || g[1] < 0 || g[2] < 0 || g[2] >= g[3] || g[2] % tile != 0)
+            return set_error(PD_INVALID_ARGUMENT, "plan_from_arrays: segment %d is malformed", s);
+    }
+    pd_plan* plan = new pd_plan();
+    plan->num_ctas = num_ctas;
+    plan->tile = tile;
+    plan->num_items = num_items;
+    plan->segments.assign(segments, segments + 4 * static_cast<size_t>(num_segments));
+    plan->cta_seg_begin.assign(cta_seg_begin, cta_seg_begin + num_ctas + 1);
+    plan->item_seg_begin.assign(item_seg_begin, item_seg_begin + num_items + 1);
+    *out = plan;
+    return PD_OK;
+}
+
 void pd_plan_free(pd_plan* plan) { delete plan; }
 int pd_plan_num_ctas(const pd_plan* p) { return p->num_ctas; }
 int pd_plan_tile(const pd_plan* p) { return p->tile; }
