@@ -198,6 +198,14 @@ void   pd_cache_destroy(pd_cache* c);
 int    pd_cache_admit(pd_cache* c);   /* slot, or -1 when every slot is in use */
 /* PD_OK, PD_OUT_OF_PAGES (nothing changed), PD_INVALID_ARGUMENT, PD_LENGTH_ERROR */
 int    pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, int n, void* stream);
+/* PagedKVCache::append (src/decode/paged_kv_cache.cu:95-136) for a whole decode step: `count` slots,
+ * slot i receives n[i] tokens from d_k[i] / d_v[i].  Allocator decisions are those of `count`
+ * single appends in the given order; one packed host->device copy and two launches instead of one
+ * copy, one launch and one stream synchronisation per slot; all-or-nothing on PD_OUT_OF_PAGES /
+ * PD_LENGTH_ERROR / PD_INVALID_ARGUMENT (a slot may appear once).  Stream-ordered: it does not
+ * wait, and the sources must stay valid until the stream has consumed them. */
+int    pd_cache_append_batch(pd_cache* c, int count, const int* slots, const void* const* d_k,
+                             const void* const* d_v, const int* n, void* stream);
 int    pd_cache_release(pd_cache* c, int slot);
 void   pd_cache_shuffle_free_pages(pd_cache* c, unsigned seed);
 int    pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads, int num_ctas, void* stream);

@@ -91,6 +91,7 @@ SIGNATURES = {
     "pd_cache_destroy": (None, [_vp]),
     "pd_cache_admit": (C.c_int, [_vp]),
     "pd_cache_append": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_int, _vp]),
+    "pd_cache_append_batch": (C.c_int, [_vp, C.c_int, _i32p, C.POINTER(_vp), C.POINTER(_vp), _i32p, _vp]),
     "pd_cache_release": (C.c_int, [_vp, C.c_int]),
     "pd_cache_shuffle_free_pages": (None, [_vp, C.c_uint]),
     "pd_cache_plan": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, C.c_int, _vp]),

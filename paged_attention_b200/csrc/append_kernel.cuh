@@ -85,4 +85,19 @@ append_batch_kernel(const AppendJob* __restrict__ jobs, int num_jobs, int total_
     }
 }
 
+// Applies a step's block-table and length updates: (slot, index, page) triples, then (slot, length) pairs.
+__global__ void __launch_bounds__(256)
+apply_updates_kernel(const int* __restrict__ table_updates, int num_table, const int* __restrict__ len_updates,
+                     int num_len, int* block_table, int table_stride, int* seq_lens)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < num_table) {
+        const int slot = table_updates[3 * i], index = table_updates[3 * i + 1], page = table_updates[3 * i + 2];
+        block_table[static_cast<size_t>(slot) * table_stride + index] = page;
+    } else if (i < num_table + num_len) {
+        const int j = i - num_table;
+        seq_lens[len_updates[2 * j]] = len_updates[2 * j + 1];
+    }
+}
+
 }  // namespace pdk

@@ -43,6 +43,12 @@ constexpr int OSTRIDE  = HEAD_DIM + 4;   // padded row of the cross-warp merge s
 constexpr int FLAG_LOAD_ONLY = 0x100;
 constexpr int FLAG_NO_L2_HINT = 0x200;
 
+// pd_params::needs_merge: 0 = no row is split, 1 = run merge_segments_kernel after the decode
+// kernel (any workspace of [segments][group][129] floats will do), 2 = the decode kernel merges
+// itself; the workspace then carries one zeroed int per (row, kv head) after the LSE array.
+constexpr int MERGE_SEPARATE  = 1;
+constexpr int MERGE_IN_KERNEL = 2;
+
 constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a tile
 constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
 constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
@@ -71,8 +77,12 @@ struct Shape {
     static constexpr int PASSES      = GROUP > 4 ? 2 : 1;
     static constexpr int MERGE_BYTES = (C::WARPS * GROUP_PAD * OSTRIDE + 2 * C::WARPS * 8) * 4;
     static constexpr int BAR_BYTES   = 2 * C::STAGES * 8 + 16;
+    // One slot of query rows per stage: the producer copies a segment's [GROUP][128] fp16 rows
+    // along with the segment's first tile, so consumers never wait on a global load of Q.
+    static constexpr int Q_SLOT_BYTES = GROUP * HEAD_DIM * 2;
+    static constexpr int Q_BYTES      = C::STAGES * Q_SLOT_BYTES;
     // +1024: the pipeline is aligned to the 128B-swizzle period by hand
-    static constexpr int SMEM_BYTES  = 1024 + PIPE_BYTES + MERGE_BYTES + BAR_BYTES;
+    static constexpr int SMEM_BYTES  = 1024 + PIPE_BYTES + Q_BYTES + MERGE_BYTES + BAR_BYTES;
     static_assert(GROUP >= 1 && GROUP <= 8, "a KV group fills the 8 columns of one MMA");
 };
 
@@ -139,6 +149,21 @@ __device__ __forceinline__ void tma_load_5d_nohint(uint32_t dst, const CUtensorM
                  " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
+// Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -191,6 +216,94 @@ __device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
     return row_off + (((c ^ (row_off >> 7)) & 7) << 4);
 }
 
+// LSE-weighted mean of the normalised partials of one (row, query head), by one warp:
+//   out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max)      (base-2 LSE)
+// Partials are read past L1 (.cg): another SM wrote them.
+template<int GROUP>
+__device__ __forceinline__ void merge_one_head(const pd_params& p, int b, int hq, int s0, int s1, int lane)
+{
+    const int gq = hq % GROUP;
+    float lse_max = -INFINITY;
+    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * GROUP + gq));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
+
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (int base = s0; base < s1; base += 32) {
+        const int s = base + lane;
+        const float w_mine = s < s1 ? exp2f(__ldcg(p.partial_lse + s * GROUP + gq) - lse_max) : 0.f;
+        const int n = min(32, s1 - base);
+        for (int j = 0; j < n; j++) {
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(
+                p.partial_out + (static_cast<size_t>(base + j) * GROUP + gq) * HEAD_DIM + lane * 4));
+            num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
+            num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
+            den += w;
+        }
+    }
+    const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
+    const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + (static_cast<size_t>(b) * p.num_q_heads + hq) * HEAD_DIM + lane * 4) = packed;
+}
+
+// All GROUP query heads of one (row, kv head) by one warp, with the loads of the heads in flight
+// together: used by the decode kernel's own merge, where the merging warp holds up its CTA's
+// pipeline until it is done.  Up to 32 segments per row in the fast path.
+template<int GROUP>
+__device__ __forceinline__ void merge_item(const pd_params& p, int b, int kv_head, int s0, int s1, int lane)
+{
+    const int n = s1 - s0;
+    if (n > 32) {
+        for (int hd = 0; hd < GROUP; hd++) merge_one_head<GROUP>(p, b, kv_head * GROUP + hd, s0, s1, lane);
+        return;
+    }
+    float w[GROUP], den[GROUP];
+#pragma unroll
+    for (int hd = 0; hd < GROUP; hd++)
+        w[hd] = lane < n ? __ldcg(p.partial_lse + (s0 + lane) * GROUP + hd) : -INFINITY;   // LSE of segment s0 + lane
+#pragma unroll
+    for (int hd = 0; hd < GROUP; hd++) {
+        float mx = w[hd];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        w[hd] = exp2f(w[hd] - mx);                                                         // 0 for lanes >= n
+        den[hd] = 0.f;
+    }
+    float4 num[GROUP];
+#pragma unroll
+    for (int hd = 0; hd < GROUP; hd++) num[hd] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
+    for (int j = 0; j < n; j++) {
+        float4 o[GROUP];
+#pragma unroll
+        for (int hd = 0; hd < GROUP; hd++)
+            o[hd] = __ldcg(reinterpret_cast<const float4*>(
+                p.partial_out + (static_cast<size_t>(s0 + j) * GROUP + hd) * HEAD_DIM + lane * 4));
+#pragma unroll
+        for (int hd = 0; hd < GROUP; hd++) {
+            const float wj = __shfl_sync(0xffffffffu, w[hd], j);
+            num[hd].x = fmaf(wj, o[hd].x, num[hd].x); num[hd].y = fmaf(wj, o[hd].y, num[hd].y);
+            num[hd].z = fmaf(wj, o[hd].z, num[hd].z); num[hd].w = fmaf(wj, o[hd].w, num[hd].w);
+            den[hd] += wj;   // same order of additions as merge_one_head: both merges give the same bits
+        }
+    }
+#pragma unroll
+    for (int hd = 0; hd < GROUP; hd++) {
+        const __half2 lo = __floats2half2_rn(num[hd].x / den[hd], num[hd].y / den[hd]);
+        const __half2 hi = __floats2half2_rn(num[hd].z / den[hd], num[hd].w / den[hd]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__half*>(p.out)
+            + (static_cast<size_t>(b) * p.num_q_heads + kv_head * GROUP + hd) * HEAD_DIM + lane * 4) = packed;
+    }
+}
+
 // ---- decode kernel ---------------------------------------------------------------
 
 template<typename KV, int GROUP, typename C>
@@ -210,11 +323,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     extern __shared__ unsigned char smem_raw[];
     const uint32_t pipe = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* gen = smem_raw + (pipe - smem_u32(smem_raw));   // generic view of the aligned base
-    float* w_o = reinterpret_cast<float*>(gen + S::PIPE_BYTES);
+    const uint32_t q_slots = pipe + S::PIPE_BYTES;                              // [STAGES][GROUP][128] halves
+    float* w_o = reinterpret_cast<float*>(gen + S::PIPE_BYTES + S::Q_BYTES);
     float* w_m = w_o + C::WARPS * S::GROUP_PAD * OSTRIDE;
     float* w_l = w_m + C::WARPS * 8;
-    const uint32_t bars = pipe + S::PIPE_BYTES + S::MERGE_BYTES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + S::PIPE_BYTES + S::MERGE_BYTES + 2 * STAGES * 8 + 8);
+    const uint32_t bars = pipe + S::PIPE_BYTES + S::Q_BYTES + S::MERGE_BYTES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + S::PIPE_BYTES + S::Q_BYTES + S::MERGE_BYTES + 2 * STAGES * 8 + 8);
     auto full_bar  = [&](int s) { return bars + s * 8; };
     auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
     const uint32_t sync_bar = bars + 2 * STAGES * 8;   // consumer-warp rendezvous (bounded, unlike bar.sync)
@@ -266,7 +380,14 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             if (*abort_flag) return false;
             const int valid = min(S::TILE, sg.w - tile_tok);
             const int nb = (valid + bt_tokens - 1) >> btl;
-            if (lane == 0) mbar_expect_tx(full_bar(stage), 2u * nb * box_bytes);
+            const bool first_tile = tile_tok == sg.z;     // the segment's query rows ride along
+            if (lane == 0) {
+                mbar_expect_tx(full_bar(stage), 2u * nb * box_bytes + (first_tile ? S::Q_SLOT_BYTES : 0));
+                if (first_tile)
+                    bulk_load(q_slots + stage * S::Q_SLOT_BYTES,
+                              static_cast<const __half*>(p.q) + (static_cast<size_t>(sg.x) * p.num_q_heads + sg.y * GROUP) * HEAD_DIM,
+                              S::Q_SLOT_BYTES, full_bar(stage));
+            }
             __syncwarp();
             const uint32_t k_dst = pipe + stage * S::STAGE_BYTES;
             const uint32_t v_dst = k_dst + S::TILE_BYTES;
@@ -368,27 +489,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 
     for (int seg = seg_begin; alive && seg < seg_end; seg++) {
         const int4 sg = __ldg(segments + seg);
-        // ---- Q fragments: column n = g is query head g of the group (zero when g >= GROUP).
-        {
-            const bool live = g < GROUP;
-            const __half* qrow = static_cast<const __half*>(p.q)
-                + (static_cast<size_t>(sg.x) * p.num_q_heads + sg.y * GROUP + (live ? g : 0)) * HEAD_DIM;
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
-                if constexpr (FP8) {
-                    // k-slots {2qd,2qd+1,2qd+8,2qd+9} of k-step ks are dims db..db+3 (one fp8 word of K)
-                    const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
-                    const uint2 v = *reinterpret_cast<const uint2*>(qrow + db);
-                    qb[ks][0] = live ? v.x : 0u;
-                    qb[ks][1] = live ? v.y : 0u;
-                } else {
-                    const uint32_t lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd);
-                    const uint32_t hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd);
-                    qb[ks][0] = live ? lo : 0u;
-                    qb[ks][1] = live ? hi : 0u;
-                }
-            }
-        }
+        bool need_q = true;   // Q^T fragments are read from the slot of the segment's first tile
 #pragma unroll
         for (int mt = 0; mt < 8; mt++) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
         m_run[0] = m_run[1] = -INFINITY;
@@ -398,6 +499,27 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const int stage = c_stage;
             if (!mbar_wait(full_bar(stage), c_phase)) { if (lane == 0) fail(ST_FULL_TIMEOUT); alive = false; break; }
             if (*abort_flag) { alive = false; break; }
+            if (need_q) {
+                // column n = g is query head g of the group (zero when g >= GROUP)
+                need_q = false;
+                const bool live = g < GROUP;
+                const uint32_t qrow = q_slots + stage * S::Q_SLOT_BYTES + (live ? g : 0) * (HEAD_DIM * 2);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    if constexpr (FP8) {
+                        // k-slots {2qd,2qd+1,2qd+8,2qd+9} of k-step ks are dims db..db+3 (one fp8 word of K)
+                        const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
+                        const uint2 v = lds64(qrow + db * 2);
+                        qb[ks][0] = live ? v.x : 0u;
+                        qb[ks][1] = live ? v.y : 0u;
+                    } else {
+                        const uint32_t lo = lds32(qrow + (ks * 16 + 2 * qd) * 2);
+                        const uint32_t hi = lds32(qrow + (ks * 16 + 8 + 2 * qd) * 2);
+                        qb[ks][0] = live ? lo : 0u;
+                        qb[ks][1] = live ? hi : 0u;
+                    }
+                }
+            }
             const uint32_t k_tile = pipe + stage * S::STAGE_BYTES;
             const uint32_t v_tile = k_tile + S::TILE_BYTES;
             const int valid = sg.w - tok;   // tokens of this tile that exist (may exceed TILE)
@@ -589,6 +711,23 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 }
                 if (!consumer_sync()) break;   // scratch is rewritten by the next pass / segment
             }
+            if (alive && !whole && p.needs_merge == MERGE_IN_KERNEL) {
+                // Last one in merges: every consumer warp of every segment of this (row, kv head)
+                // publishes its partial stores and counts itself; the warp that completes the count
+                // finds all partials visible and combines them, then re-arms the counter.
+                const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
+                int* counter = reinterpret_cast<int*>(p.partial_lse + static_cast<size_t>(p.cta_seg_begin[p.num_ctas]) * GROUP) + item;
+                __threadfence();
+                __syncwarp();
+                int seen = 0;
+                if (lane == 0) seen = atomicAdd(counter, 1);
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                if (seen == (s1 - s0) * C::WARPS - 1) {
+                    __threadfence();
+                    merge_item<GROUP>(p, sg.x, sg.y, s0, s1, lane);
+                    if (lane == 0) *counter = 0;
+                }
+            }
         }
     }
 }
@@ -608,36 +747,9 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     if (idx >= p.batch * p.num_q_heads) return;
     const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
     const int item = b * p.num_kv_heads + hq / GROUP;
-    const int gq = hq % GROUP;
     const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
-
-    float lse_max = -INFINITY;
-    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, p.partial_lse[s * GROUP + gq]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
-
-    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.f;
-    for (int base = s0; base < s1; base += 32) {
-        const int s = base + lane;
-        const float w_mine = s < s1 ? exp2f(p.partial_lse[s * GROUP + gq] - lse_max) : 0.f;
-        const int n = min(32, s1 - base);
-        for (int j = 0; j < n; j++) {
-            const float w = __shfl_sync(0xffffffffu, w_mine, j);
-            const float4 o = *reinterpret_cast<const float4*>(
-                p.partial_out + (static_cast<size_t>(base + j) * GROUP + gq) * HEAD_DIM + lane * 4);
-            num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
-            num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
-            den += w;
-        }
-    }
-    const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
-    const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
-    uint2 packed;
-    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
-    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + (static_cast<size_t>(b) * p.num_q_heads + hq) * HEAD_DIM + lane * 4) = packed;
+    merge_one_head<GROUP>(p, b, hq, s0, s1, lane);
 }
 
 }  // namespace pdk

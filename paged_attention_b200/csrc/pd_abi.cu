@@ -373,6 +373,11 @@ struct pd_cache {
     std::vector<std::vector<int>> tables;
     std::vector<int> seq_lens;
     std::vector<char> occupied;
+    // batched append: pinned staging + device copy of the step's job list, grow-only
+    void*  batch_staging = nullptr;
+    void*  batch_device = nullptr;
+    size_t batch_cap = 0;
+    cudaEvent_t batch_staged = nullptr;
 };
 
 extern "C" {
@@ -529,9 +534,11 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     if (total) PD_CUDA(cudaMemcpyAsync(dp->arena, dp->staging, total, cudaMemcpyHostToDevice, stream));
     PD_CUDA(cudaEventRecord(dp->staged, stream));
 
-    // Workspace for split rows: [segments][group][head_dim] outputs then [segments][group] LSEs.
+    // Workspace for split rows: [segments][group][head_dim] outputs, [segments][group] LSEs, then
+    // one arrival counter per (row, kv head) for the in-kernel merge (zero between launches: the
+    // merging warp re-arms its counter).
     const size_t rows = nseg * group;
-    const size_t need = rows * (head_dim + 1);
+    const size_t need = rows * (head_dim + 1) + plan->num_items;
     if (need > dp->partial_cap) {
         PD_CUDA(cudaFree(dp->partial));
         dp->partial = nullptr; dp->partial_cap = 0;
@@ -546,7 +553,11 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     dp->partial_lse    = dp->partial ? dp->partial + rows * head_dim : nullptr;
     dp->num_ctas       = plan->num_ctas;
     dp->num_segments   = static_cast<int>(nseg);
-    dp->needs_merge    = static_cast<int>(nseg) > plan->num_items ? 1 : 0;
+    dp->needs_merge    = static_cast<int>(nseg) > plan->num_items ? pdk::MERGE_IN_KERNEL : 0;
+    static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
+    if (dp->needs_merge && separate_merge) dp->needs_merge = pdk::MERGE_SEPARATE;
+    if (dp->needs_merge && plan->num_items)
+        PD_CUDA(cudaMemsetAsync(dp->partial + rows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     return PD_OK;
 }
 
@@ -577,6 +588,8 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: null device pointer");
     if (p->needs_merge && (!p->partial_out || !p->partial_lse))
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: split rows need the partial workspace");
+    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode: q must be 16-byte aligned");
     if (int rc = configure(k)) return rc;
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -597,7 +610,7 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
               btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
               status, stream);
     PD_CUDA(cudaGetLastError());
-    if (p->needs_merge) {
+    if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, stream);
         PD_CUDA(cudaGetLastError());
     }
@@ -685,9 +698,12 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     const StaticScratch* scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
 
+    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: q must be 16-byte aligned");
     pd_params local = *p;                       // same launch, workspace redirected to the built-in array
     local.partial_out = scratch->partials;
     local.partial_lse = scratch->partials + rows * p->head_dim;
+    local.needs_merge = p->needs_merge ? pdk::MERGE_SEPARATE : 0;   // the built-in array carries no arrival counters
 
     const unsigned box_tokens = gcd_u(static_cast<unsigned>(p->page_size), static_cast<unsigned>(k->tile));
     int btl = 0;
@@ -786,6 +802,9 @@ void pd_cache_destroy(pd_cache* c) {
     cudaFree(c->d_block_table);
     cudaFree(c->d_seq_lens);
     cudaFree(c->d_slot_ids);
+    if (c->batch_staged) { cudaEventSynchronize(c->batch_staged); cudaEventDestroy(c->batch_staged); }
+    cudaFreeHost(c->batch_staging);
+    cudaFree(c->batch_device);
     pd_plan_free(c->plan);
     pd_device_plan_destroy(c->device_plan);
     delete c;
@@ -871,6 +890,107 @@ int pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, int
         return rc;
     // As in the reference (src/decode/paged_kv_cache.cu:133-134) the call returns with the tokens in place.
     PD_CUDA(cudaStreamSynchronize(stream));
+    return PD_OK;
+}
+
+// One decode step's appends for many slots: the allocator runs for every slot in the order given
+// (so block tables come out exactly as from the same pd_cache_append calls in that order), then
+// ONE packed host->device copy carries the job list, the new block-table entries and the new
+// lengths, and two launches apply them: table/length updates, then the token scatter for all
+// slots at once.  All-or-nothing: if the pool cannot hold every slot's tokens nothing changes.
+// Stream-ordered: returns without waiting; the K/V sources must stay valid until the stream
+// has run the scatter.
+int pd_cache_append_batch(pd_cache* c, int count, const int* slots, const void* const* d_k, const void* const* d_v,
+                          const int* n, void* stream_) {
+    if (!c || count < 0 || (count > 0 && (!slots || !d_k || !d_v || !n)))
+        return set_error(PD_INVALID_ARGUMENT, "append_batch: bad argument");
+    if (count == 0) return PD_OK;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int ps = c->cfg.page_size;
+    // ---- validate everything before touching the allocator
+    long long new_pages = 0, total_units = 0;
+    std::vector<char> seen(c->cfg.max_slots, 0);
+    for (int i = 0; i < count; i++) {
+        const int slot = slots[i];
+        if (slot < 0 || slot >= c->cfg.max_slots || !c->occupied[slot])
+            return set_error(PD_INVALID_ARGUMENT, "append_batch: slot is not admitted");
+        if (seen[slot]) return set_error(PD_INVALID_ARGUMENT, "append_batch: slot %d appears twice", slot);
+        seen[slot] = 1;
+        if (n[i] < 0) return set_error(PD_INVALID_ARGUMENT, "append_batch: negative token count");
+        if (n[i] == 0) continue;
+        if (!d_k[i] || !d_v[i] || (reinterpret_cast<uintptr_t>(d_k[i]) | reinterpret_cast<uintptr_t>(d_v[i])) % 16 != 0)
+            return set_error(PD_INVALID_ARGUMENT, "append_batch: K/V sources must be non-null and 16-byte aligned");
+        const int need = (c->seq_lens[slot] + n[i] + ps - 1) / ps;
+        if (need > c->cfg.max_pages_per_slot) return set_error(PD_LENGTH_ERROR, "append: sequence exceeds max_pages_per_slot");
+        new_pages += need - static_cast<int>(c->tables[slot].size());
+        total_units += static_cast<long long>(n[i]) * c->cfg.num_kv_heads * 16;
+    }
+    if (total_units > 0x7fffffffLL) return set_error(PD_LENGTH_ERROR, "append_batch: too many tokens in one batch");
+    if (new_pages > static_cast<long long>(c->free_pages.size())) return set_error(PD_OUT_OF_PAGES, "append: out of pages");
+
+    // ---- packed buffer: jobs | (slot, index, page) table updates | (slot, length) updates
+    struct TableUpdate { int slot, index, page; };
+    struct LenUpdate { int slot, len; };
+    auto round16 = [](size_t x) { return (x + 15) & ~static_cast<size_t>(15); };
+    const size_t jobs_bytes = round16(sizeof(pdk::AppendJob) * count);
+    const size_t tab_bytes  = round16(sizeof(TableUpdate) * static_cast<size_t>(new_pages));
+    const size_t len_bytes  = round16(sizeof(LenUpdate) * count);
+    const size_t total = jobs_bytes + tab_bytes + len_bytes;
+    if (!c->batch_staged) PD_CUDA(cudaEventCreateWithFlags(&c->batch_staged, cudaEventDisableTiming));
+    else PD_CUDA(cudaEventSynchronize(c->batch_staged));      // the previous batch still reads the staging buffer
+    if (total > c->batch_cap) {
+        PD_CUDA(cudaFreeHost(c->batch_staging));
+        PD_CUDA(cudaFree(c->batch_device));
+        c->batch_staging = c->batch_device = nullptr; c->batch_cap = 0;
+        const size_t cap = std::max<size_t>(total * 2, 4096);
+        PD_CUDA(cudaMallocHost(&c->batch_staging, cap));
+        PD_CUDA(cudaMalloc(&c->batch_device, cap));
+        c->batch_cap = cap;
+    }
+    char* h = static_cast<char*>(c->batch_staging);
+    auto* jobs = reinterpret_cast<pdk::AppendJob*>(h);
+    auto* tabs = reinterpret_cast<TableUpdate*>(h + jobs_bytes);
+    auto* lens = reinterpret_cast<LenUpdate*>(h + jobs_bytes + tab_bytes);
+    long long units = 0;
+    int t = 0, live = 0;
+    for (int i = 0; i < count; i++) {
+        const int slot = slots[i];
+        const int old_len = c->seq_lens[slot];
+        const int have = static_cast<int>(c->tables[slot].size());
+        const int need = (old_len + n[i] + ps - 1) / ps;
+        for (int j = have; j < need; j++) {
+            const int page = c->free_pages.back();
+            c->free_pages.pop_back();
+            c->tables[slot].push_back(page);
+            tabs[t++] = TableUpdate{slot, j, page};
+        }
+        c->seq_lens[slot] = old_len + n[i];
+        lens[i] = LenUpdate{slot, c->seq_lens[slot]};
+        if (n[i] == 0) continue;
+        jobs[live++] = pdk::AppendJob{static_cast<const __half*>(d_k[i]), static_cast<const __half*>(d_v[i]),
+                                      c->d_block_table + static_cast<size_t>(slot) * c->cfg.max_pages_per_slot,
+                                      old_len, n[i], static_cast<int>(units)};
+        units += static_cast<long long>(n[i]) * c->cfg.num_kv_heads * 16;
+    }
+    PD_CUDA(cudaMemcpyAsync(c->batch_device, c->batch_staging, total, cudaMemcpyHostToDevice, stream));
+    PD_CUDA(cudaEventRecord(c->batch_staged, stream));
+    char* d = static_cast<char*>(c->batch_device);
+    pdk::apply_updates_kernel<<<(t + count + 255) / 256, 256, 0, stream>>>(
+        reinterpret_cast<const int*>(d + jobs_bytes), t, reinterpret_cast<const int*>(d + jobs_bytes + tab_bytes), count,
+        c->d_block_table, c->cfg.max_pages_per_slot, c->d_seq_lens);
+    PD_CUDA(cudaGetLastError());
+    if (live > 0) {
+        const int blocks = static_cast<int>(std::min<long long>((units + 255) / 256, 148 * 16));
+        const bool fp8 = c->cfg.dtype == PD_FP8_E4M3;
+        const float ik = fp8 ? 1.f / c->cfg.k_scale : 1.f, iv = fp8 ? 1.f / c->cfg.v_scale : 1.f;
+        if (fp8)
+            pdk::append_batch_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<const pdk::AppendJob*>(d), live,
+                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv);
+        else
+            pdk::append_batch_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<const pdk::AppendJob*>(d), live,
+                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv);
+        PD_CUDA(cudaGetLastError());
+    }
     return PD_OK;
 }
 

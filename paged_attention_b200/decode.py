@@ -234,6 +234,21 @@ class PagedKVCache:
         check(rc)
         return True
 
+    def append_batch(self, slots, d_ks, d_vs, ns, stream=0):
+        """One decode step's appends for many slots in one call (stream-ordered, no host wait).
+        True when appended, False (nothing changed) when the pool cannot hold all of them."""
+        count = len(slots)
+        s = np.ascontiguousarray(slots, dtype=np.int32)
+        n = np.ascontiguousarray(ns, dtype=np.int32)
+        ks = (C.c_void_p * count)(*[_ptr(x) for x in d_ks])
+        vs = (C.c_void_p * count)(*[_ptr(x) for x in d_vs])
+        rc = _lib.lib().pd_cache_append_batch(self._h, count, s.ctypes.data_as(C.POINTER(C.c_int)), ks, vs,
+                                              n.ctypes.data_as(C.POINTER(C.c_int)), stream)
+        if rc == _lib.PD_OUT_OF_PAGES:
+            return False
+        check(rc)
+        return True
+
     def release(self, slot):
         check(_lib.lib().pd_cache_release(self._h, slot))
 
