@@ -10,8 +10,10 @@ workload names; pages are scattered through a pool sized exactly to fit.
 
 N > 1 (launched by torch.distributed.run, one rank per GPU): by default the batch
 is sharded, every rank holds its own full-size layer shard (weak scaling) and the
-outputs are all-gathered over NCCL inside the timed step; `--shard heads` splits
-the KV heads of one fixed problem instead (strong scaling, workload c5).
+outputs are gathered inside the timed step - by default by the decode kernel itself
+(peer stores into every rank's buffer, `--gather peer`), or by ncclAllGather
+(`--gather nccl`); `--shard heads` splits the KV heads of one fixed problem instead
+(strong scaling, workload c5).
 
 `--impl reference` times the reference's own CPU attention (compiled from its
 sources into oracle/_ref, else the oracle port) on a bounded sample of the same
@@ -262,7 +264,27 @@ def our_arm(args, wl):
     out_host = torch.empty_like(q_host).pin_memory()
     q = q_host.cuda()
     out = torch.zeros_like(q)
-    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device="cuda") if world > 1 else None
+    # N > 1: the outputs of all ranks are put together inside the step.  "peer" (default): the decode
+    # kernel stores its rows into every peer's gathered buffer and a one-warp kernel waits for the
+    # peers' flags; "nccl": decode into a local buffer, then ncclAllGather.
+    gather_mode = args.gather if world > 1 else "none"
+    gathered, gg, gathered_views = None, None, None
+    rows_total = l_B if shard == "heads" else l_B * world
+    heads_total = l_hq * world if shard == "heads" else l_hq
+    full_bytes = rows_total * heads_total * 128 * 2
+    if gather_mode == "nccl":
+        gathered = torch.empty((world * l_B, l_hq, 128), dtype=out.dtype, device="cuda")
+    elif gather_mode == "peer":
+        from paged_attention_b200.sharding import GatherGroup
+        gg = GatherGroup(full_bytes)
+        head_off = rank * l_hq if shard == "heads" else 0
+        row_off = 0 if shard == "heads" else rank * l_B
+
+        class _Dev:   # zero-copy torch view of the library's gathered buffers
+            def __init__(self, ptr, n):
+                self.__cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+        gathered_views = [torch.as_tensor(_Dev(gg.buffer_ptr(i), full_bytes), device="cuda") for i in (0, 1)]
+        full_host = torch.empty(full_bytes, dtype=torch.uint8).pin_memory()
 
     # Drive the kernel through the plan API, as a serving engine does: plan once per step, run per layer.
     plan = pa.make_plan(pa.KVDtype(dtype), lens, l_hq, l_hkv, 128, args.ctas)
@@ -279,9 +301,16 @@ def our_arm(args, wl):
     def flush():   # read-only pass over 4x L2: the next kernel starts cold and L2 holds no dirty lines
         pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)
 
+    step_counter = [0]
+
     def step():
+        step_counter[0] += 1
+        if gather_mode == "peer":
+            gg.decode(pa.KVDtype(dtype), params, heads_total, head_off, row_off, stream, cfg.num_pages)
+            gg.wait(stream)
+            return
         pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
-        if world > 1:
+        if gather_mode == "nccl":
             dist.all_gather_into_tensor(gathered, out)
 
     def step_decode_only():
@@ -292,12 +321,21 @@ def our_arm(args, wl):
     def step_e2e():
         q.copy_(q_host, non_blocking=True)
         step()
-        out_host.copy_(out if world == 1 else gathered[rank], non_blocking=True)
+        if gather_mode == "peer":     # the whole gathered result of this step comes back to the host
+            full_host.copy_(gathered_views[step_counter[0] & 1], non_blocking=True)
+        elif gather_mode == "nccl":
+            out_host.copy_(gathered[rank * l_B:(rank + 1) * l_B], non_blocking=True)
+        else:
+            out_host.copy_(out, non_blocking=True)
+
+    rendezvous = torch.zeros(1, device="cuda")
 
     def timed(fn, steps):
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         for s, e in ev:
             flush()
+            if world > 1:      # device-side rendezvous: all ranks enter the step together, so one rank's
+                dist.all_reduce(rendezvous)   # slower flush is not charged to the others' step
             s.record()
             fn()
             e.record()
@@ -351,22 +389,27 @@ def our_arm(args, wl):
             "data": "synthetic",
             "config": {"workload": desc, "name": args.workload, "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
                        "kv_heads_per_gpu": l_hkv, "page_size": page, "sharding": "none" if world == 1 else shard,
+                       "gather": {"none": "single GPU", "peer": "decode kernel stores into every peer's buffer (NVLink peer stores) + flag wait kernel",
+                                  "nccl": "ncclAllGather after the decode"}[gather_mode],
                        "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
                        "ctas": plan.num_ctas, "segments": plan.num_segments, "tile": plan.tile,
                        "kernel_variant": pa.kernel_variant(),
                        "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
                              % (local_bytes / 1e6),
                        "timing": "CUDA events around decode+merge%s per step, summed over steps, max over ranks"
-                                 % (" + NCCL all-gather" if world > 1 else "")},
+                                 % (" + output gather; ranks rendezvous (1-element all-reduce) after the flush, before the start event" if world > 1 else "")},
             "algorithmic_bytes_per_step": job_bytes,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "kernel": "paged_decode_kernel",
                          "kernel_ms": per_decode, "frac_of_8TBps_nominal": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": per_e2e,
-                    "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": full_bytes if gather_mode == "peer" else out_host.numel() * 2,
                     "note": "pinned q -> device, decode+merge, out -> pinned host, per step; the KV cache is resident state"},
-            "gpu_launches": args.steps * ((2 if needs_merge else 1) + 1),
-            "gpu_launches_note": "per step: paged_decode_kernel%s + stream_read_kernel (L2 flush)" % (" + merge_segments_kernel" if needs_merge else ""),
+            "gpu_launches": args.steps * (2 + (1 if gather_mode == "peer" else 0) + (1 if needs_merge == 1 else 0)),
+            "gpu_launches_note": "per step: paged_decode_kernel (split rows merged in-kernel)%s%s + stream_read_kernel (L2 flush)"
+                                 % (" + merge_segments_kernel" if needs_merge == 1 else "",
+                                    " + gather_wait_kernel" if gather_mode == "peer" else ""),
             "clocks": clocks, "wall_s_timed_region": wall,
         }
         if cpu:
@@ -379,6 +422,9 @@ def our_arm(args, wl):
                 line["roofline"]["traffic"] = t["dram_bytes_per_launch"]
                 line["roofline"]["traffic_source"] = t["source"]
         print(json.dumps(line))
+    if gg is not None:
+        dist.barrier()
+        gg.close()
     cache.close()
     if world > 1:
         dist.destroy_process_group()
@@ -392,6 +438,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--shard", default=None, choices=["batch", "heads"])
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--variant", type=int, default=None)
     ap.add_argument("--contiguous-pages", action="store_true")

@@ -177,6 +177,39 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
  * Nonzero encodes (code << 24 | cta) of the first wait that gave up. */
 int pd_kernel_status(void* stream, unsigned* status);
 
+/* Multi-GPU (no counterpart in the reference, which is single-GPU): the decode layer sharded over
+ * the GPUs of one node, one process per GPU, with the output all-gather done by the decode
+ * kernel itself.  Every rank owns a gathered-output buffer; the kernel's epilogue (and its
+ * in-kernel merge) stores each output row into that buffer on EVERY peer with plain peer stores
+ * over NVLink, and the last CTA raises a per-rank flag on every peer, then waits (bounded, ~1 s,
+ * then PD_KERNEL_TIMEOUT via pd_kernel_status) until all peers' flags of the current step have
+ * arrived.  No NCCL call, no multicast.
+ *   pd_gather_create   allocates this rank's block (two alternating output buffers + flags)
+ *   pd_gather_export   writes the block's CUDA IPC handle (pd_gather_handle_bytes() bytes)
+ *   pd_gather_connect  takes all ranks' handles, rank-major, and maps the peers' blocks
+ *   pd_paged_decode_gather  pd_paged_decode_bounded with gathered output: this rank's
+ *       [batch][num_q_heads] rows land at row `row_offset`, head `head_offset` of rows of
+ *       `row_stride_heads` heads (kv-head sharding: offset = rank * local heads; batch sharding:
+ *       row_offset = first global row).  p->out is ignored.  Plans with split rows must be
+ *       bound by pd_device_plan_bind (in-kernel merge).
+ *   pd_gather_buffer   the local gathered buffer of step parity `which` (0/1; -1 = last step) */
+typedef struct pd_gather_group pd_gather_group;
+int      pd_gather_create(int world, int rank, size_t out_bytes, pd_gather_group** out);
+void     pd_gather_destroy(pd_gather_group* g);
+int      pd_gather_handle_bytes(void);
+int      pd_gather_export(const pd_gather_group* g, unsigned char* handle);
+int      pd_gather_connect(pd_gather_group* g, const unsigned char* all_handles);
+void*    pd_gather_buffer(const pd_gather_group* g, int which);
+unsigned pd_gather_epoch(const pd_gather_group* g);
+int      pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g,
+                                int row_stride_heads, int head_offset, int row_offset, void* stream);
+int      pd_gather_wait(pd_gather_group* g, void* stream);
+/* By default the decode kernel's last CTA itself waits (bounded) for all peers' flags before the
+ * kernel ends, and pd_gather_wait has nothing left to do; with `on` = 0 the kernel only signals
+ * and pd_gather_wait enqueues the separate one-warp wait kernel (for callers that want other
+ * work between the decode and the point where the gathered rows are needed). */
+int      pd_gather_set_wait_in_kernel(pd_gather_group* g, int on);
+
 /* read_kernel of the reference's benchmark (bench/bench_decode.cu:69-78, "copy" mode
  * :224-240): a read-only streaming pass over `bytes` of device memory with `blocks`
  * CTAs of 512 threads; the attainable HBM read rate decode is compared with. */

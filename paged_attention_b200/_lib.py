@@ -82,6 +82,16 @@ SIGNATURES = {
     "pd_paged_decode_bounded": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp]),
     "pd_paged_decode_static": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, C.c_int, _vp, _vp]),
     "pd_kernel_status": (C.c_int, [_vp, C.POINTER(C.c_uint)]),
+    "pd_gather_create": (C.c_int, [C.c_int, C.c_int, C.c_size_t, C.POINTER(_vp)]),
+    "pd_gather_destroy": (None, [_vp]),
+    "pd_gather_handle_bytes": (C.c_int, []),
+    "pd_gather_export": (C.c_int, [_vp, C.c_char_p]),
+    "pd_gather_connect": (C.c_int, [_vp, C.c_char_p]),
+    "pd_gather_buffer": (_vp, [_vp, C.c_int]),
+    "pd_gather_epoch": (C.c_uint, [_vp]),
+    "pd_paged_decode_gather": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "pd_gather_wait": (C.c_int, [_vp, _vp]),
+    "pd_gather_set_wait_in_kernel": (C.c_int, [_vp, C.c_int]),
     "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
     "pd_append_tokens": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_float, C.c_float, _vp]),

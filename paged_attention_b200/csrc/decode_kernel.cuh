@@ -53,6 +53,39 @@ constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a til
 constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
 constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
 constexpr unsigned ST_SYNC_TIMEOUT  = 4;   // a consumer warp gave up waiting for its siblings
+constexpr unsigned ST_GATHER_TIMEOUT = 5;  // a peer's "slice has landed" flag never arrived
+
+// Where outputs go.  world == 0: to pd_params::out, [batch][num_q_heads][128].  world > 0: this
+// GPU's rows are one slice of a layout gathered over `world` GPUs of the node, and every output
+// is stored straight into the gathered buffer of every peer (plain peer stores over NVLink; the
+// local buffer is out[rank]).  When the last CTA of the grid is done, flags[r][rank] = epoch tells
+// peer r that this rank's slice has landed.  No collective call follows the kernel.
+constexpr int MAX_GATHER = 8;
+struct GatherOut {
+    int       world;
+    int       rank;
+    int       row_stride;    // query heads per row of the gathered layout
+    int       head_offset;   // first head of this rank's slice within a row (kv-head sharding)
+    int       row_offset;    // first row of this rank's slice (batch sharding)
+    unsigned  epoch;
+    int       wait_in_kernel;   // the grid's last CTA also waits (bounded) for every peer's flag before it exits
+    __half*   out[MAX_GATHER];
+    unsigned* flags[MAX_GATHER];
+    unsigned* done;          // CTA arrival counter in local memory, zero between launches
+};
+
+__device__ __forceinline__ size_t out_index(const pd_params& p, const GatherOut& gp, int row, int head) {
+    return gp.world ? (static_cast<size_t>(row + gp.row_offset) * gp.row_stride + head + gp.head_offset) * 128
+                    : (static_cast<size_t>(row) * p.num_q_heads + head) * 128;
+}
+template<typename T>
+__device__ __forceinline__ void store_out(const pd_params& p, const GatherOut& gp, size_t index, T value) {
+    if (gp.world == 0) {
+        *reinterpret_cast<T*>(static_cast<__half*>(p.out) + index) = value;
+    } else {
+        for (int r = 0; r < gp.world; r++) *reinterpret_cast<T*>(gp.out[r] + index) = value;
+    }
+}
 
 template<int WARPS_, int GROUPS_PER_WARP_, int STAGES_, int MIN_CTAS_>
 struct Config {
@@ -220,7 +253,7 @@ __device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
 //   out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max)      (base-2 LSE)
 // Partials are read past L1 (.cg): another SM wrote them.
 template<int GROUP>
-__device__ __forceinline__ void merge_one_head(const pd_params& p, int b, int hq, int s0, int s1, int lane)
+__device__ __forceinline__ void merge_one_head(const pd_params& p, const GatherOut& gp, int b, int hq, int s0, int s1, int lane)
 {
     const int gq = hq % GROUP;
     float lse_max = -INFINITY;
@@ -248,18 +281,18 @@ __device__ __forceinline__ void merge_one_head(const pd_params& p, int b, int hq
     uint2 packed;
     packed.x = *reinterpret_cast<const uint32_t*>(&lo);
     packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(static_cast<__half*>(p.out) + (static_cast<size_t>(b) * p.num_q_heads + hq) * HEAD_DIM + lane * 4) = packed;
+    store_out(p, gp, out_index(p, gp, b, hq) + lane * 4, packed);
 }
 
 // All GROUP query heads of one (row, kv head) by one warp, with the loads of the heads in flight
 // together: used by the decode kernel's own merge, where the merging warp holds up its CTA's
 // pipeline until it is done.  Up to 32 segments per row in the fast path.
 template<int GROUP>
-__device__ __forceinline__ void merge_item(const pd_params& p, int b, int kv_head, int s0, int s1, int lane)
+__device__ __forceinline__ void merge_item(const pd_params& p, const GatherOut& gp, int b, int kv_head, int s0, int s1, int lane)
 {
     const int n = s1 - s0;
     if (n > 32) {
-        for (int hd = 0; hd < GROUP; hd++) merge_one_head<GROUP>(p, b, kv_head * GROUP + hd, s0, s1, lane);
+        for (int hd = 0; hd < GROUP; hd++) merge_one_head<GROUP>(p, gp, b, kv_head * GROUP + hd, s0, s1, lane);
         return;
     }
     float w[GROUP], den[GROUP];
@@ -299,8 +332,38 @@ __device__ __forceinline__ void merge_item(const pd_params& p, int b, int kv_hea
         uint2 packed;
         packed.x = *reinterpret_cast<const uint32_t*>(&lo);
         packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(static_cast<__half*>(p.out)
-            + (static_cast<size_t>(b) * p.num_q_heads + kv_head * GROUP + hd) * HEAD_DIM + lane * 4) = packed;
+        store_out(p, gp, out_index(p, gp, b, kv_head * GROUP + hd) + lane * 4, packed);
+    }
+}
+
+// Called by one thread per CTA after the CTA's outputs are stored and fenced.  The CTA that
+// completes the count re-arms the counter and raises this rank's flag on every peer.
+__device__ __forceinline__ void signal_peers(const GatherOut& gp, unsigned* status) {
+    const unsigned seen = atomicAdd(gp.done, 1u);
+    if (seen == gridDim.x - 1) {
+        *gp.done = 0;
+        __threadfence_system();
+        for (int r = 0; r < gp.world; r++) {
+            volatile unsigned* f = gp.flags[r] + gp.rank;
+            *f = gp.epoch;
+        }
+        if (gp.wait_in_kernel) {
+            // The kernel ends only when every peer's slice has landed here too, so the stream that
+            // ran it may read the gathered buffer next.  Bounded like every other wait.
+            const volatile unsigned* mine = gp.flags[gp.rank];
+            const long long t0 = clock64();
+            for (int r = 0; r < gp.world; r++) {
+                while (static_cast<int>(mine[r] - gp.epoch) < 0) {
+                    if (clock64() - t0 > (1ll << 31)) {
+                        atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
+                        return;
+                    }
+                    __nanosleep(64);
+                }
+            }
+            // peers' rows arrived through this GPU's L2; the kernel boundary that follows is what
+            // later readers order against, so no further fence is needed here
+        }
     }
 }
 
@@ -310,7 +373,7 @@ template<typename KV, int GROUP, typename C>
 __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const int btl_flags /* log2(box tokens) | diagnostic flags */,
-                    unsigned* __restrict__ status)
+                    unsigned* __restrict__ status, const __grid_constant__ GatherOut gp)
 {
     const int  btl     = btl_flags & 0xff;
     const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
@@ -335,7 +398,10 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 
     const int seg_begin = p.cta_seg_begin[blockIdx.x];
     const int seg_end   = p.cta_seg_begin[blockIdx.x + 1];
-    if (seg_begin >= seg_end) return;
+    if (seg_begin >= seg_end) {
+        if (gp.world && threadIdx.x == 0) signal_peers(gp, status);   // an idle CTA still counts towards "grid done"
+        return;
+    }
 
     const int tid  = threadIdx.x;
     const int warp = tid >> 5;
@@ -702,7 +768,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                     }
                     const float o = num / den * p.v_scale;
                     if (whole) {
-                        static_cast<__half*>(p.out)[(static_cast<size_t>(sg.x) * p.num_q_heads + sg.y * GROUP + hd) * HEAD_DIM + d] = __float2half(o);
+                        store_out(p, gp, out_index(p, gp, sg.x, sg.y * GROUP + hd) + d, __float2half(o));
                     } else {
                         const size_t row = static_cast<size_t>(seg) * GROUP + hd;
                         p.partial_out[row * HEAD_DIM + d] = o;
@@ -724,11 +790,18 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 seen = __shfl_sync(0xffffffffu, seen, 0);
                 if (seen == (s1 - s0) * C::WARPS - 1) {
                     __threadfence();
-                    merge_item<GROUP>(p, sg.x, sg.y, s0, s1, lane);
+                    merge_item<GROUP>(p, gp, sg.x, sg.y, s0, s1, lane);
                     if (lane == 0) *counter = 0;
                 }
             }
         }
+    }
+    if (gp.world && alive) {
+        // Gathered output: this CTA's stores are ordered before its count (device scope); the CTA
+        // that completes the count issues the one system-scope fence ahead of the flags, which by
+        // cumulativity covers every store counted before it.
+        __threadfence();
+        if (consumer_sync() && tid == 0) signal_peers(gp, status);
     }
 }
 
@@ -749,7 +822,27 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     const int item = b * p.num_kv_heads + hq / GROUP;
     const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
-    merge_one_head<GROUP>(p, b, hq, s0, s1, lane);
+    GatherOut local{};   // world = 0: plain output
+    merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane);
+}
+
+// Waits (bounded) until every peer's flag has reached `epoch`: their slices are in this GPU's
+// gathered buffer.  One warp, lane r watches peer r.  Gives up after about a second and records
+// ST_GATHER_TIMEOUT << 24 | peer in the status word; the context stays usable.
+__global__ void gather_wait_kernel(const unsigned* flags, int world, unsigned epoch, unsigned* status)
+{
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    const volatile unsigned* f = flags + r;
+    const long long t0 = clock64();
+    while (static_cast<int>(*f - epoch) < 0) {
+        if (clock64() - t0 > (1ll << 31)) {
+            atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
+            break;
+        }
+        __nanosleep(100);
+    }
+    __threadfence_system();
 }
 
 }  // namespace pdk

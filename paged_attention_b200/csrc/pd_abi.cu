@@ -76,15 +76,15 @@ constexpr int NUM_VARIANTS = 5;
 struct KernelInfo {
     const void* fn;
     int tile, threads, smem, per_sm;
-    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, cudaStream_t);
+    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&, cudaStream_t);
     void (*merge)(const pd_params&, cudaStream_t);
 };
 
 template<typename KV, int GROUP, typename C>
 void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl,
-                   unsigned* status, cudaStream_t stream) {
+                   unsigned* status, const pdk::GatherOut& gather, cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
-    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status);
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather);
 }
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
@@ -575,7 +575,10 @@ int pd_device_plan_bind(const pd_device_plan* dp, pd_params* p) {
 
 // ---- decode -----------------------------------------------------------------------------------------------
 
-int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream_) {
+}  // extern "C"
+
+namespace {
+int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherOut& gather, void* stream_) {
     if (!p) return set_error(PD_INVALID_ARGUMENT, "paged_decode: null params");
     if (p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
         return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
@@ -583,8 +586,10 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
     if (int rc = find_kernel(dtype, p->head_dim, p->num_q_heads / p->num_kv_heads, &k)) return rc;
     if (p->page_size <= 0) return set_error(PD_INVALID_ARGUMENT, "page_size must be positive");
     if (p->num_ctas <= 0 || p->batch <= 0) return PD_OK;   // empty plan: nothing to do
-    if (!p->q || !p->out || !p->k_cache || !p->v_cache || !p->block_table || !p->segments || !p->cta_seg_begin ||
-        !p->item_seg_begin)
+    if (gather.world && p->needs_merge == pdk::MERGE_SEPARATE)
+        return set_error(PD_INVALID_ARGUMENT, "gathered output needs the in-kernel merge (bind the plan with pd_device_plan_bind)");
+    if (!p->q || (!p->out && !gather.world) || !p->k_cache || !p->v_cache || !p->block_table || !p->segments ||
+        !p->cta_seg_begin || !p->item_seg_begin)
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: null device pointer");
     if (p->needs_merge && (!p->partial_out || !p->partial_lse))
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: split rows need the partial workspace");
@@ -608,13 +613,20 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
     static const int stage_limit = std::getenv("PD_B200_STAGE_LIMIT") ? (std::atoi(std::getenv("PD_B200_STAGE_LIMIT")) & 0xf) : 0;
     k->launch(*p, k_map, v_map,
               btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
-              status, stream);
+              status, gather, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, stream);
         PD_CUDA(cudaGetLastError());
     }
     return PD_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream) {
+    return decode_impl(dtype, p, num_pages, pdk::GatherOut{}, stream);
 }
 
 int pd_paged_decode(int dtype, const pd_params* p, void* stream) {
@@ -713,7 +725,7 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, stream);
+    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, stream);
     PD_CUDA(cudaGetLastError());
     if (local.needs_merge) {
         k->merge(local, stream);
@@ -781,6 +793,133 @@ int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache,
     else
         pdk::append_kernel<true><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size,
                                                              1.f / k_scale, 1.f / v_scale);
+    PD_CUDA(cudaGetLastError());
+    return PD_OK;
+}
+
+// ---- outputs gathered over the GPUs of a node by peer stores ---------------------------------------------------
+//
+// One process per GPU.  Each rank allocates one block: two gathered-output buffers (alternating
+// per step, so a fast rank never overwrites what a slow peer is still reading from the previous
+// step), one flag per peer, one CTA counter.  Blocks are exchanged as CUDA IPC handles; after
+// pd_gather_connect every rank can store into every peer's block.
+
+} // extern "C"
+
+struct pd_gather_group {
+    int world = 0, rank = 0;
+    size_t out_bytes = 0, block_bytes = 0;
+    unsigned epoch = 0;
+    bool wait_in_kernel = true;
+    char* block[pdk::MAX_GATHER] = {};      // block[rank] is the local allocation, the rest are IPC mappings
+    bool connected = false;
+    size_t flags_offset() const { return 2 * out_bytes; }
+    size_t done_offset() const { return 2 * out_bytes + 128; }
+};
+
+extern "C" {
+
+int pd_gather_create(int world, int rank, size_t out_bytes, pd_gather_group** out) {
+    if (!out || world < 1 || world > pdk::MAX_GATHER || rank < 0 || rank >= world || out_bytes == 0)
+        return set_error(PD_INVALID_ARGUMENT, "gather_create: world must be 1..%d, rank inside it, out_bytes positive", pdk::MAX_GATHER);
+    pd_gather_group* g = new pd_gather_group();
+    g->world = world; g->rank = rank;
+    g->out_bytes = (out_bytes + 255) & ~static_cast<size_t>(255);
+    g->block_bytes = 2 * g->out_bytes + 256;
+    void* b = nullptr;
+    cudaError_t e = cudaMalloc(&b, g->block_bytes);
+    if (e == cudaSuccess) e = cudaMemset(b, 0, g->block_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(b);
+        delete g;
+        return set_error(PD_CUDA_ERROR, "gather_create: %s", cudaGetErrorString(e));
+    }
+    g->block[rank] = static_cast<char*>(b);
+    g->connected = world == 1;
+    *out = g;
+    return PD_OK;
+}
+
+void pd_gather_destroy(pd_gather_group* g) {
+    if (!g) return;
+    for (int r = 0; r < g->world; r++) {
+        if (!g->block[r]) continue;
+        if (r == g->rank) cudaFree(g->block[r]);
+        else cudaIpcCloseMemHandle(g->block[r]);
+    }
+    delete g;
+}
+
+int pd_gather_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+
+int pd_gather_export(const pd_gather_group* g, unsigned char* handle) {
+    if (!g || !handle) return set_error(PD_INVALID_ARGUMENT, "gather_export: null argument");
+    cudaIpcMemHandle_t h;
+    PD_CUDA(cudaIpcGetMemHandle(&h, g->block[g->rank]));
+    std::memcpy(handle, &h, sizeof h);
+    return PD_OK;
+}
+
+int pd_gather_connect(pd_gather_group* g, const unsigned char* all_handles) {
+    if (!g || !all_handles) return set_error(PD_INVALID_ARGUMENT, "gather_connect: null argument");
+    for (int r = 0; r < g->world; r++) {
+        if (r == g->rank || g->block[r]) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, all_handles + static_cast<size_t>(r) * sizeof h, sizeof h);
+        void* ptr = nullptr;
+        PD_CUDA(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        g->block[r] = static_cast<char*>(ptr);
+    }
+    g->connected = true;
+    return PD_OK;
+}
+
+void* pd_gather_buffer(const pd_gather_group* g, int which) {
+    if (!g) return nullptr;
+    const unsigned parity = which < 0 ? (g->epoch & 1u) : static_cast<unsigned>(which & 1);
+    return g->block[g->rank] + parity * g->out_bytes;
+}
+
+unsigned pd_gather_epoch(const pd_gather_group* g) { return g ? g->epoch : 0; }
+
+int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g, int row_stride_heads,
+                           int head_offset, int row_offset, void* stream) {
+    if (!g || !p) return set_error(PD_INVALID_ARGUMENT, "decode_gather: null argument");
+    if (!g->connected) return set_error(PD_INVALID_ARGUMENT, "decode_gather: call pd_gather_connect first");
+    if (row_stride_heads < p->num_q_heads + head_offset || head_offset < 0 || row_offset < 0)
+        return set_error(PD_INVALID_ARGUMENT, "decode_gather: this rank's slice does not fit the gathered row");
+    const size_t last = (static_cast<size_t>(p->batch + row_offset) * row_stride_heads) * 128 * sizeof(__half);
+    if (last > g->out_bytes) return set_error(PD_INVALID_ARGUMENT, "decode_gather: gathered layout exceeds the buffer");
+    if (p->num_ctas <= 0 || p->batch <= 0) return set_error(PD_INVALID_ARGUMENT, "decode_gather: empty plan");
+    g->epoch++;
+    pdk::GatherOut go{};
+    go.world = g->world; go.rank = g->rank;
+    go.row_stride = row_stride_heads; go.head_offset = head_offset; go.row_offset = row_offset;
+    go.epoch = g->epoch;
+    go.wait_in_kernel = g->wait_in_kernel ? 1 : 0;
+    for (int r = 0; r < g->world; r++) {
+        go.out[r]   = reinterpret_cast<__half*>(g->block[r] + (g->epoch & 1u) * g->out_bytes);
+        go.flags[r] = reinterpret_cast<unsigned*>(g->block[r] + g->flags_offset());
+    }
+    go.done = reinterpret_cast<unsigned*>(g->block[g->rank] + g->done_offset());
+    const int rc = decode_impl(dtype, p, num_pages, go, stream);
+    if (rc != PD_OK) g->epoch--;
+    return rc;
+}
+
+int pd_gather_set_wait_in_kernel(pd_gather_group* g, int on) {
+    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather: null argument");
+    g->wait_in_kernel = on != 0;
+    return PD_OK;
+}
+
+int pd_gather_wait(pd_gather_group* g, void* stream) {
+    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_wait: null argument");
+    if (g->wait_in_kernel) return PD_OK;   // the decode kernel already waited before it ended
+    unsigned* status = nullptr;
+    if (int rc = status_word(&status)) return rc;
+    pdk::gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()), g->world, g->epoch, status);
     PD_CUDA(cudaGetLastError());
     return PD_OK;
 }

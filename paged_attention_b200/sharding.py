@@ -92,3 +92,55 @@ def gather_outputs(out_local, mode, group=None, rows=None):
         gathered = gathered.view((world, widest) + tuple(padded.shape[1:]))
         return torch.cat([gathered[r, :rows[r]] for r in range(world)], dim=0)
     raise ValueError("mode must be 'heads' or 'batch'")
+
+
+class GatherGroup:
+    """Gathered outputs without a collective call: every rank's decode kernel stores its rows into
+    every peer's buffer (peer stores over NVLink) and raises a flag; `wait` enqueues the bounded
+    flag wait.  One process per GPU; the IPC handles travel through the torch process group."""
+
+    def __init__(self, out_bytes, group=None):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.out_bytes = out_bytes
+        h = C.c_void_p()
+        _lib.check(_lib.lib().pd_gather_create(self.world, self.rank, out_bytes, C.byref(h)))
+        self._h = h
+        n = _lib.lib().pd_gather_handle_bytes()
+        mine = C.create_string_buffer(n)
+        _lib.check(_lib.lib().pd_gather_export(h, mine))
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, mine.raw, group=group)
+            _lib.check(_lib.lib().pd_gather_connect(h, b"".join(handles)))
+            dist.barrier(group)        # every rank has mapped every block before anyone stores
+        torch.cuda.synchronize()
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.lib().pd_gather_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def decode(self, dtype, params, row_stride_heads, head_offset=0, row_offset=0, stream=0, num_pages=0):
+        self._lib.check(self._lib.lib().pd_paged_decode_gather(int(dtype), self._C.byref(params), num_pages, self._h,
+                                                               row_stride_heads, head_offset, row_offset, stream))
+
+    def set_wait_in_kernel(self, on):
+        """on (default): the decode kernel ends only when all peers' rows have landed; off: it only
+        signals and `wait` enqueues a separate wait kernel."""
+        self._lib.check(self._lib.lib().pd_gather_set_wait_in_kernel(self._h, int(bool(on))))
+
+    def wait(self, stream=0):
+        self._lib.check(self._lib.lib().pd_gather_wait(self._h, stream))
+
+    def buffer_ptr(self, which=-1):
+        """Device pointer of the local gathered buffer (which = 0/1, -1 = the one the last decode filled)."""
+        return self._lib.lib().pd_gather_buffer(self._h, which)
