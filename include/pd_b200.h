@@ -204,6 +204,11 @@ unsigned pd_gather_epoch(const pd_gather_group* g);
 int      pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g,
                                 int row_stride_heads, int head_offset, int row_offset, void* stream);
 int      pd_gather_wait(pd_gather_group* g, void* stream);
+/* The same wait for a step the caller names (steps are numbered 1, 2, ... by pd_gather_epoch): lets a
+ * pipelined caller wait for step k's rows while step k+1 is already in flight.  Waiting for a step
+ * that no peer ever signals ends after the bounded ~1 s with PD_KERNEL_TIMEOUT in pd_kernel_status;
+ * the context stays usable. */
+int      pd_gather_wait_epoch(pd_gather_group* g, unsigned epoch, void* stream);
 /* By default the decode kernel's last CTA itself waits (bounded) for all peers' flags before the
  * kernel ends, and pd_gather_wait has nothing left to do; with `on` = 0 the kernel only signals
  * and pd_gather_wait enqueues the separate one-warp wait kernel (for callers that want other

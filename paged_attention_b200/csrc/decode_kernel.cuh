@@ -407,6 +407,10 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
+    if (tid == C::WARPS * 32) {   // producer lane 0: have the descriptors on their way before the first copy needs them
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&k_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&v_map) : "memory");
+    }
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), C::WARPS); }
         mbar_init(sync_bar, C::WARPS);

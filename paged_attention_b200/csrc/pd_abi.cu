@@ -369,6 +369,7 @@ struct pd_cache {
     pd_plan* plan = nullptr;
     pd_device_plan* device_plan = nullptr;
     int plan_batch = 0, plan_num_q_heads = 0;
+    bool plan_identity = false;
     std::vector<int> free_pages;
     std::vector<std::vector<int>> tables;
     std::vector<int> seq_lens;
@@ -554,8 +555,15 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     dp->num_ctas       = plan->num_ctas;
     dp->num_segments   = static_cast<int>(nseg);
     dp->needs_merge    = static_cast<int>(nseg) > plan->num_items ? pdk::MERGE_IN_KERNEL : 0;
+    // The in-kernel merge is done by ONE warp per split row; that is the cheaper way while rows are
+    // cut in a few pieces (a long batch: 2-3 segments per row), but a row cut in dozens of pieces
+    // (one long sequence spread over the whole grid) merges faster in the separate kernel, which
+    // puts a warp on every (row, query head).
+    int widest = 0;
+    for (int i = 0; i < plan->num_items; i++)
+        widest = std::max(widest, plan->item_seg_begin[i + 1] - plan->item_seg_begin[i]);
     static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
-    if (dp->needs_merge && separate_merge) dp->needs_merge = pdk::MERGE_SEPARATE;
+    if (dp->needs_merge && (separate_merge || widest > 4)) dp->needs_merge = pdk::MERGE_SEPARATE;
     if (dp->needs_merge && plan->num_items)
         PD_CUDA(cudaMemsetAsync(dp->partial + rows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     return PD_OK;
@@ -586,8 +594,6 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     if (int rc = find_kernel(dtype, p->head_dim, p->num_q_heads / p->num_kv_heads, &k)) return rc;
     if (p->page_size <= 0) return set_error(PD_INVALID_ARGUMENT, "page_size must be positive");
     if (p->num_ctas <= 0 || p->batch <= 0) return PD_OK;   // empty plan: nothing to do
-    if (gather.world && p->needs_merge == pdk::MERGE_SEPARATE)
-        return set_error(PD_INVALID_ARGUMENT, "gathered output needs the in-kernel merge (bind the plan with pd_device_plan_bind)");
     if (!p->q || (!p->out && !gather.world) || !p->k_cache || !p->v_cache || !p->block_table || !p->segments ||
         !p->cta_seg_begin || !p->item_seg_begin)
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: null device pointer");
@@ -902,7 +908,12 @@ int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gath
         go.flags[r] = reinterpret_cast<unsigned*>(g->block[r] + g->flags_offset());
     }
     go.done = reinterpret_cast<unsigned*>(g->block[g->rank] + g->done_offset());
-    const int rc = decode_impl(dtype, p, num_pages, go, stream);
+    // Gathered rows are written by the decode kernel itself, so split rows are merged in-kernel here
+    // even where the plan preferred the separate merge kernel; workspaces bound by
+    // pd_device_plan_bind always carry the arrival counters that needs.
+    pd_params local = *p;
+    if (local.needs_merge) local.needs_merge = pdk::MERGE_IN_KERNEL;
+    const int rc = decode_impl(dtype, &local, num_pages, go, stream);
     if (rc != PD_OK) g->epoch--;
     return rc;
 }
@@ -913,15 +924,20 @@ int pd_gather_set_wait_in_kernel(pd_gather_group* g, int on) {
     return PD_OK;
 }
 
-int pd_gather_wait(pd_gather_group* g, void* stream) {
+int pd_gather_wait_epoch(pd_gather_group* g, unsigned epoch, void* stream) {
     if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_wait: null argument");
-    if (g->wait_in_kernel) return PD_OK;   // the decode kernel already waited before it ended
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
     pdk::gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()), g->world, g->epoch, status);
+        reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()), g->world, epoch, status);
     PD_CUDA(cudaGetLastError());
     return PD_OK;
+}
+
+int pd_gather_wait(pd_gather_group* g, void* stream) {
+    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_wait: null argument");
+    if (g->wait_in_kernel) return PD_OK;   // the decode kernel already waited before it ended
+    return pd_gather_wait_epoch(g, g->epoch, stream);
 }
 
 // ---- PagedKVCache ---------------------------------------------------------------------------------------------
@@ -1195,6 +1211,8 @@ int pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads,
         PD_CUDA(cudaMemcpyAsync(c->d_slot_ids, slots, sizeof(int) * num_slots, cudaMemcpyHostToDevice, stream));
     c->plan_batch = num_slots;
     c->plan_num_q_heads = num_q_heads;
+    c->plan_identity = true;
+    for (int i = 0; i < num_slots; i++) c->plan_identity = c->plan_identity && slots[i] == i;
     return PD_OK;
 }
 
@@ -1205,7 +1223,7 @@ int pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream) {
     pd_cache_params(c, &p);
     p.q = d_q;
     p.out = d_out;
-    p.slot_ids = c->d_slot_ids;
+    p.slot_ids = c->plan_identity ? nullptr : c->d_slot_ids;   // row i reads slot i: skip the indirection
     p.batch = c->plan_batch;
     p.num_q_heads = c->plan_num_q_heads;
     pd_device_plan_bind(c->device_plan, &p);

@@ -141,6 +141,14 @@ class GatherGroup:
     def wait(self, stream=0):
         self._lib.check(self._lib.lib().pd_gather_wait(self._h, stream))
 
+    def wait_epoch(self, epoch, stream=0):
+        """Wait (bounded) for the rows of step `epoch`; see `epoch` for the current step number."""
+        self._lib.check(self._lib.lib().pd_gather_wait_epoch(self._h, epoch, stream))
+
+    @property
+    def epoch(self):
+        return self._lib.lib().pd_gather_epoch(self._h)
+
     def buffer_ptr(self, which=-1):
         """Device pointer of the local gathered buffer (which = 0/1, -1 = the one the last decode filled)."""
         return self._lib.lib().pd_gather_buffer(self._h, which)

@@ -114,6 +114,27 @@ def test_gather_single_rank(torch_cuda, pa):
     cache.close()
 
 
+def test_wait_for_a_flag_nobody_sets_times_out_and_the_context_survives(torch_cuda, pa):
+    """Failure detection without a fault: the bounded wait for a step that no rank ever signals gives up
+    after about a second, the status word reports which peer was missing, and the next decode on the same
+    context works."""
+    import time
+    from common import TOL
+    from paged_attention_b200 import sharding
+    torch = torch_cuda
+    got, gg, cache = _run_rank(0, 1, torch, pa, sharding, "heads")
+    t0 = time.time()
+    gg.wait_epoch(gg.epoch + 1)            # nothing will ever raise the flag to this value
+    with pytest.raises(pa.decode._lib.KernelTimeout, match="wait 5"):
+        pa.kernel_status()
+    assert 0.2 < time.time() - t0 < 10.0
+    assert pa.kernel_status() == 0          # reading the status re-arms it
+    got2, gg2, cache2 = _run_rank(0, 1, torch, pa, sharding, "batch")
+    assert np.abs(got2 - _oracle_full()).max() < TOL
+    for x in (gg, gg2, cache, cache2):
+        x.close()
+
+
 def _worker(rank, world, port, out_dir):
     sys.path.insert(0, HERE)
     sys.path.insert(0, os.path.dirname(HERE))
