@@ -397,9 +397,11 @@ def our_arm(args, wl):
             "metric": "paged_decode_achieved_hbm_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": per_step,
             "us_per_layer": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "f16 mma, f32 accumulate (KV %s)" % ("fp16" if dtype == 0 else "fp8_e4m3"),
+            "dtype": "f16",
             "data": "synthetic",
-            "config": {"workload": desc, "name": args.workload, "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
+            "config": {"workload": desc, "name": args.workload,
+                       "arithmetic": "mma.m16n8k16 f16 x f16 -> f32 accumulate, softmax in f32; KV stored as %s"
+                                     % ("fp16" if dtype == 0 else "fp8 e4m3, widened to f16 in registers"), "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
                        "kv_heads_per_gpu": l_hkv, "page_size": page, "sharding": "none" if world == 1 else shard,
                        "gather": {"none": "single GPU", "peer": "decode kernel stores into every peer's buffer (NVLink peer stores) + flag wait kernel",
                                   "nccl": "ncclAllGather after the decode"}[gather_mode],

@@ -183,7 +183,7 @@ int pd_kernel_status(void* stream, unsigned* status);
  * in-kernel merge) stores each output row into that buffer on EVERY peer with plain peer stores
  * over NVLink, and the last CTA raises a per-rank flag on every peer, then waits (bounded, ~1 s,
  * then PD_KERNEL_TIMEOUT via pd_kernel_status) until all peers' flags of the current step have
- * arrived.  No NCCL call, no multicast.
+ * arrived.  No collective library call is involved.
  *   pd_gather_create   allocates this rank's block (two alternating output buffers + flags)
  *   pd_gather_export   writes the block's CUDA IPC handle (pd_gather_handle_bytes() bytes)
  *   pd_gather_connect  takes all ranks' handles, rank-major, and maps the peers' blocks
