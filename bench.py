@@ -272,11 +272,27 @@ def our_arm(args, wl):
     rows_total = l_B if shard == "heads" else l_B * world
     heads_total = l_hq * world if shard == "heads" else l_hq
     full_bytes = rows_total * heads_total * 128 * 2
+    gather_note = None
+    if gather_mode == "peer":
+        # Peer stores need CUDA IPC mappings between all GPUs of the node.  If any rank cannot set them
+        # up, every rank falls back to ncclAllGather (and the JSON line says so).
+        from paged_attention_b200.sharding import GatherGroup
+        ok = torch.ones(1, device="cuda")
+        try:
+            gg = GatherGroup(full_bytes)
+        except Exception as e:
+            ok.zero_()
+            gather_note = "peer setup failed (%s); fell back to ncclAllGather" % str(e)[:120]
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            if gg is not None:
+                gg.close()
+                gg = None
+            gather_mode = "nccl"
+            gather_note = gather_note or "a peer could not set up IPC mappings; fell back to ncclAllGather"
     if gather_mode == "nccl":
         gathered = torch.empty((world * l_B, l_hq, 128), dtype=out.dtype, device="cuda")
     elif gather_mode == "peer":
-        from paged_attention_b200.sharding import GatherGroup
-        gg = GatherGroup(full_bytes)
         head_off = rank * l_hq if shard == "heads" else 0
         row_off = 0 if shard == "heads" else rank * l_B
 
@@ -404,7 +420,7 @@ def our_arm(args, wl):
                                      % ("fp16" if dtype == 0 else "fp8 e4m3, widened to f16 in registers"), "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
                        "kv_heads_per_gpu": l_hkv, "page_size": page, "sharding": "none" if world == 1 else shard,
                        "gather": {"none": "single GPU", "peer": "decode kernel stores into every peer's buffer (NVLink peer stores) + flag wait kernel",
-                                  "nccl": "ncclAllGather after the decode"}[gather_mode],
+                                  "nccl": "ncclAllGather after the decode"}[gather_mode] + (" [" + gather_note + "]" if gather_note else ""),
                        "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
                        "ctas": plan.num_ctas, "segments": plan.num_segments, "tile": plan.tile,
                        "kernel_variant": pa.kernel_variant(),

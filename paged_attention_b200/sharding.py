@@ -108,17 +108,37 @@ class GatherGroup:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.out_bytes = out_bytes
-        h = C.c_void_p()
-        _lib.check(_lib.lib().pd_gather_create(self.world, self.rank, out_bytes, C.byref(h)))
-        self._h = h
+        # Set-up is collective: every step below is followed by an exchange of "did it work", so that a
+        # rank that cannot allocate or map a peer makes ALL ranks raise instead of leaving the others
+        # waiting in a collective.
+        self._h = None
+        err = None
         n = _lib.lib().pd_gather_handle_bytes()
         mine = C.create_string_buffer(n)
-        _lib.check(_lib.lib().pd_gather_export(h, mine))
+        try:
+            h = C.c_void_p()
+            _lib.check(_lib.lib().pd_gather_create(self.world, self.rank, out_bytes, C.byref(h)))
+            self._h = h
+            _lib.check(_lib.lib().pd_gather_export(h, mine))
+        except Exception as e:
+            err = e
         if self.world > 1:
             handles = [None] * self.world
-            dist.all_gather_object(handles, mine.raw, group=group)
-            _lib.check(_lib.lib().pd_gather_connect(h, b"".join(handles)))
-            dist.barrier(group)        # every rank has mapped every block before anyone stores
+            dist.all_gather_object(handles, (mine.raw, err is None), group=group)
+            if err is None and all(ok for _, ok in handles):
+                try:
+                    _lib.check(_lib.lib().pd_gather_connect(self._h, b"".join(hb for hb, _ in handles)))
+                except Exception as e:
+                    err = e
+            elif err is None:
+                err = RuntimeError("a peer could not create its gather block")
+            oks = [None] * self.world
+            dist.all_gather_object(oks, err is None, group=group)   # also: everyone has mapped every block
+            if err is None and not all(oks):
+                err = RuntimeError("a peer could not map the gather blocks")
+        if err is not None:
+            self.close()
+            raise err
         torch.cuda.synchronize()
 
     def close(self):
