@@ -220,16 +220,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
                                        : promo_env == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
                                                         : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     CUresult r;
-    static const bool exp_noswz = std::getenv("PD_B200_EXP_NOSWIZZLE") != nullptr;   // EXPERIMENT
-    if (dtype == PD_FP16 && exp_noswz) {
-        const cuuint64_t dims[5]    = {128, static_cast<cuuint64_t>(page_size), 1, static_cast<cuuint64_t>(num_kv_heads), pages};
-        const cuuint64_t strides[4] = {row, row, row * page_size, row * page_size * num_kv_heads};
-        const cuuint32_t box[5]     = {128, 1u << btl, 1, 1, 1};
-        const cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
-        r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(pool), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, promo,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (dtype == PD_FP16) {
+    if (dtype == PD_FP16) {
         const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
         const cuuint64_t strides[4] = {row, 128, row * page_size, row * page_size * num_kv_heads};
         const cuuint32_t box[5]     = {64, 1u << btl, 2, 1, 1};
