@@ -330,7 +330,7 @@ def our_arm(args, wl):
             dist.all_gather_into_tensor(gathered, out)
 
     def step_decode_only():
-        params.needs_merge = 0
+        params.needs_merge = -1      # diagnostic value: decode kernel only, split rows stay unmerged
         pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
         params.needs_merge = needs_merge
 

@@ -106,6 +106,15 @@ int pd_default_ctas(int dtype, int head_dim, int group, int* out);
  * variable PD_B200_VARIANT.  Changes pd_tile_tokens, so re-plan afterwards. */
 int pd_set_kernel_variant(int variant);
 int pd_kernel_variant(void);
+/* Second tuning knob, also without a counterpart in the reference.  fp16 layers with exactly 8 kv heads
+ * whose plan came from pd_make_plan (directly or through the cache) normally run the "head-fused"
+ * schedule: the device plan also carries the step cut by rows, a tile is 16 tokens of all 8 kv heads
+ * (one 32 KB box per page and pool for fp16 instead of eight 4 KB boxes fetched by different CTAs at
+ * different times), one consumer warp per kv head, no cross-warp merge.  The plan object and
+ * pd_params keep the reference's (row, kv head) format either way.  0 switches it off (default on;
+ * environment PD_B200_NO_HEAD_FUSED=1 also switches it off).  Re-plan after changing it. */
+int pd_set_head_fused(int on);
+int pd_head_fused(void);
 
 /* decode::make_plan (src/decode/decode.hpp:38-39).  num_ctas <= 0 uses
  * pd_default_ctas (needs a GPU).  The plan is a host object; free it with

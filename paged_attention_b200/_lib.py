@@ -63,6 +63,8 @@ SIGNATURES = {
     "pd_default_ctas": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p]),
     "pd_set_kernel_variant": (C.c_int, [C.c_int]),
     "pd_kernel_variant": (C.c_int, []),
+    "pd_set_head_fused": (C.c_int, [C.c_int]),
+    "pd_head_fused": (C.c_int, []),
     "pd_make_plan": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "pd_make_plan_tiled": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "pd_plan_from_arrays": (C.c_int, [C.c_int, C.c_int, _i32p, C.c_int, _i32p, _i32p, C.c_int, C.POINTER(_vp)]),

@@ -87,32 +87,43 @@ __device__ __forceinline__ void store_out(const pd_params& p, const GatherOut& g
     }
 }
 
-template<int WARPS_, int GROUPS_PER_WARP_, int STAGES_, int MIN_CTAS_>
+// HEADS = 1: a tile is TILE tokens of ONE kv head, the consumer warps split the tile's tokens and
+// merge their softmax states at a segment's end (the reference's (row, kv head) work items).
+// HEADS = 8 ("head-fused"): a tile is 16 tokens of ALL 8 kv heads of a row, fetched as one box per
+// page and pool (32 KB of contiguous DRAM for fp16 instead of eight separate 4 KB pieces read at
+// different times by different CTAs), consumer warp w owns kv head w outright, so nothing is merged
+// across warps and a segment ends without any CTA-wide synchronisation.  Work items are rows.
+template<int WARPS_, int GROUPS_PER_WARP_, int STAGES_, int MIN_CTAS_, int HEADS_ = 1>
 struct Config {
     static constexpr int WARPS           = WARPS_;             // consumer warps (one more warp produces)
     static constexpr int GROUPS_PER_WARP = GROUPS_PER_WARP_;   // 16-token groups per warp per tile
     static constexpr int STAGES          = STAGES_;
     static constexpr int MIN_CTAS        = MIN_CTAS_;
+    static constexpr int HEADS           = HEADS_;             // kv heads per tile
+    static_assert(HEADS_ == 1 || (HEADS_ == WARPS_ && GROUPS_PER_WARP_ == 1), "head-fused: one warp per kv head");
 };
 
 template<typename KV, int GROUP, typename C>
 struct Shape {
     static constexpr int THREADS     = (C::WARPS + 1) * 32;
     static constexpr int CONSUMERS   = C::WARPS * 32;
-    static constexpr int TILE        = C::WARPS * C::GROUPS_PER_WARP * 16;
+    static constexpr int HEADS       = C::HEADS;
+    static constexpr int TILE        = C::WARPS * C::GROUPS_PER_WARP * 16 / HEADS;   // tokens per tile
     static constexpr int ROW_BYTES   = HEAD_DIM * static_cast<int>(sizeof(KV));
-    static constexpr int TILE_BYTES  = TILE * ROW_BYTES;
+    static constexpr int TILE_BYTES  = TILE * ROW_BYTES * HEADS;
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
     static constexpr int PIPE_BYTES  = C::STAGES * STAGE_BYTES;
     // The cross-warp merge runs over at most 4 heads at a time (two passes for a
     // group of 8), which keeps two CTAs of the fp16 configuration on one SM.
     static constexpr int GROUP_PAD   = GROUP < 2 ? 2 : (GROUP > 4 ? 4 : GROUP);
     static constexpr int PASSES      = GROUP > 4 ? 2 : 1;
-    static constexpr int MERGE_BYTES = (C::WARPS * GROUP_PAD * OSTRIDE + 2 * C::WARPS * 8) * 4;
+    static constexpr int MERGE_BYTES = HEADS > 1 ? 0 : (C::WARPS * GROUP_PAD * OSTRIDE + 2 * C::WARPS * 8) * 4;
     static constexpr int BAR_BYTES   = 2 * C::STAGES * 8 + 16;
     // One slot of query rows per stage: the producer copies a segment's [GROUP][128] fp16 rows
     // along with the segment's first tile, so consumers never wait on a global load of Q.
-    static constexpr int Q_SLOT_BYTES = GROUP * HEAD_DIM * 2;
+    // (Head-fused tiles would need all query heads of a row per slot; there the consumer warps load
+    // their own rows from global memory at a segment's start instead.)
+    static constexpr int Q_SLOT_BYTES = HEADS > 1 ? 0 : GROUP * HEAD_DIM * 2;
     static constexpr int Q_BYTES      = C::STAGES * Q_SLOT_BYTES;
     // +1024: the pipeline is aligned to the 128B-swizzle period by hand
     static constexpr int SMEM_BYTES  = 1024 + PIPE_BYTES + Q_BYTES + MERGE_BYTES + BAR_BYTES;
@@ -237,11 +248,12 @@ __device__ __forceinline__ uint32_t fp8x2_to_half2(uint32_t two_bytes) {
 // Byte offset, inside one K or V tile, of the 128-byte shared-memory row that
 // holds token `t` (0..TILE-1), panel `h` (fp16: dims 64h..64h+63; fp8: h = 0).
 // A tile is a run of boxes of 2^btl tokens; a box is [panel][token][128 B].
-template<typename KV>
-__device__ __forceinline__ uint32_t row_offset(int t, int h, int btl) {
+// With HEADS kv heads per box the box is [kv head][panel][token][128 B].
+template<typename KV, int HEADS = 1>
+__device__ __forceinline__ uint32_t row_offset(int t, int h, int btl, int head = 0) {
     constexpr int PANELS = sizeof(KV);   // 2 for fp16, 1 for fp8
     const int box = t >> btl, r = t & ((1 << btl) - 1);
-    return static_cast<uint32_t>(((box * PANELS + h) << btl) + r) << 7;
+    return static_cast<uint32_t>((((box * HEADS + head) * PANELS + h) << btl) + r) << 7;
 }
 // Address of 16-byte chunk c of a 128-byte row under the TMA 128B swizzle
 // (chunk index XOR row index mod 8; the tile base is 1024-byte aligned).
@@ -249,15 +261,150 @@ __device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
     return row_off + (((c ^ (row_off >> 7)) & 7) << 4);
 }
 
+// ---- one 16-token group: S^T = K Q^T, online softmax, O^T += V^T P^T ------------------------------
+//
+// `rows(t, panel)` gives the byte offset, from the tile base, of the 128-byte shared-memory row
+// that holds token t of the group's (row, kv head), panel = dims 64*panel.. (fp16) or 0 (fp8).
+// grp_row is the first token of the group inside the tile; grp_valid (1..16+) how many of its tokens exist.
+// Returns true if it wrote to shared memory (dead V rows cleared), so the caller fences before
+// handing the stage back to the copy engine.
+template<typename KV, typename Rows>
+__device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint32_t v_tile, const Rows rows,
+                                              const int grp_row, const int grp_valid, const uint32_t (&qb)[8][2],
+                                              float (&acc)[8][4], float (&m_run)[2], float (&l_run)[2],
+                                              const float qk_scale, const int lane)
+{
+    constexpr bool FP8 = sizeof(KV) == 1;
+    const int g = lane >> 2, qd = lane & 3;
+    bool wrote = false;
+    if (grp_valid < 16) {
+        // Rows past the end hold whatever the page or the stage held before; a NaN
+        // there would survive P = 0 in the PV product, so clear V's dead rows.
+        constexpr int CH = HEAD_DIM * static_cast<int>(sizeof(KV)) / 16;
+        for (int idx = lane; idx < 16 * CH; idx += 32) {
+            const int r = idx / CH, c = idx % CH;
+            if (r >= grp_valid)
+                sts128_zero(v_tile + rows(grp_row + r, FP8 ? 0 : (c >> 3)) + ((c & 7) << 4));
+        }
+        wrote = true;
+        __syncwarp();
+    }
+
+    // ---- 1. S^T = K Q^T : 16 tokens x 8 heads, two interleaved accumulators.
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (!FP8) {
+        const int t = grp_row + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const uint32_t r0 = rows(t, 0), r1 = rows(t, 1);
+        const int hi = lane >> 4;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            uint32_t a[4];
+            ldmatrix_x4(a, k_tile + swz(ks < 4 ? r0 : r1, (ks & 3) * 2 + hi));
+            if (ks & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
+            else        mma_16816(s0, a, qb[ks][0], qb[ks][1]);
+        }
+    } else {
+        const uint32_t r0 = rows(grp_row + g, 0), r1 = rows(grp_row + g + 8, 0);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const uint4 lo = lds128(k_tile + swz(r0, 2 * qd + j));
+            const uint4 hi = lds128(k_tile + swz(r1, 2 * qd + j));
+            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                const uint32_t a[4] = {fp8x2_to_half2(wl[m] & 0xffffu), fp8x2_to_half2(wh[m] & 0xffffu),
+                                       fp8x2_to_half2(wl[m] >> 16),     fp8x2_to_half2(wh[m] >> 16)};
+                const int ks = 4 * j + m;
+                if (m & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
+                else       mma_16816(s0, a, qb[ks][0], qb[ks][1]);
+            }
+        }
+    }
+
+    // ---- 2. online softmax. This lane: tokens g, g+8 of the group, heads 2qd, 2qd+1.
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) x[i] = (s0[i] + s1[i]) * qk_scale;
+    if (grp_valid < 16) {
+        if (g >= grp_valid)     { x[0] = -INFINITY; x[1] = -INFINITY; }
+        if (g + 8 >= grp_valid) { x[2] = -INFINITY; x[3] = -INFINITY; }
+    }
+    float mx[2] = {fmaxf(x[0], x[2]), fmaxf(x[1], x[3])};
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        alpha[h] = exp2f(m_run[h] - m_new);
+        m_run[h] = m_new;
+    }
+    float pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) pr[i] = exp2f(x[i] - m_run[i & 1]);
+    l_run[0] = l_run[0] * alpha[0] + (pr[0] + pr[2]);
+    l_run[1] = l_run[1] * alpha[1] + (pr[1] + pr[3]);
+#pragma unroll
+    for (int mt = 0; mt < 8; mt++) {
+        acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
+        acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
+    }
+
+    // ---- 3. O^T += V^T P^T.  P^T's B fragment = transposed 8x8 blocks of the scores.
+    const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));   // tokens 0..7
+    const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));   // tokens 8..15
+    if constexpr (!FP8) {
+        const int t = grp_row + (lane & 7) + ((lane >> 4) & 1) * 8;
+        const uint32_t r0 = rows(t, 0), r1 = rows(t, 1);
+        const int hi = (lane >> 3) & 1;
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, v_tile + swz(mt < 4 ? r0 : r1, (mt & 3) * 2 + hi));
+            mma_16816(acc[mt], a, pb0, pb1);
+        }
+    } else {
+        // This lane: tokens 2qd, 2qd+1, 2qd+8, 2qd+9, dims 16g..16g+15.  M-tile mt has
+        // row g = dim 16g + 2mt and row g+8 = dim 16g + 2mt + 1.
+        uint32_t vw[4][4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int t = grp_row + 2 * qd + (r & 1) + (r >> 1) * 8;
+            const uint4 v = lds128(v_tile + swz(rows(t, 0), g));
+            vw[r][0] = v.x; vw[r][1] = v.y; vw[r][2] = v.z; vw[r][3] = v.w;
+        }
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            // bytes [t0 d, t1 d, t0 d+1, t1 d+1] for d = 4w (lo) and 4w+2 (hi)
+            const uint32_t lo01 = __byte_perm(vw[0][w], vw[1][w], 0x5140u);
+            const uint32_t hi01 = __byte_perm(vw[0][w], vw[1][w], 0x7362u);
+            const uint32_t lo23 = __byte_perm(vw[2][w], vw[3][w], 0x5140u);
+            const uint32_t hi23 = __byte_perm(vw[2][w], vw[3][w], 0x7362u);
+            const uint32_t a_lo[4] = {fp8x2_to_half2(lo01 & 0xffffu), fp8x2_to_half2(lo01 >> 16),
+                                      fp8x2_to_half2(lo23 & 0xffffu), fp8x2_to_half2(lo23 >> 16)};
+            const uint32_t a_hi[4] = {fp8x2_to_half2(hi01 & 0xffffu), fp8x2_to_half2(hi01 >> 16),
+                                      fp8x2_to_half2(hi23 & 0xffffu), fp8x2_to_half2(hi23 >> 16)};
+            mma_16816(acc[2 * w],     a_lo, pb0, pb1);
+            mma_16816(acc[2 * w + 1], a_hi, pb0, pb1);
+        }
+    }
+    return wrote;
+}
+
 // LSE-weighted mean of the normalised partials of one (row, query head), by one warp:
 //   out = sum_s 2^(lse_s - max) o_s / sum_s 2^(lse_s - max)      (base-2 LSE)
 // Partials are read past L1 (.cg): another SM wrote them.
 template<int GROUP>
-__device__ __forceinline__ void merge_one_head(const pd_params& p, const GatherOut& gp, int b, int hq, int s0, int s1, int lane)
+// Partial (segment s, this head) lives at index s * stride + gq: stride = GROUP, gq = hq % GROUP for
+// (row, kv head) work items; stride = num_q_heads, gq = hq for head-fused rows.
+__device__ __forceinline__ void merge_one_head(const pd_params& p, const GatherOut& gp, int b, int hq, int s0, int s1,
+                                               int lane, int stride, int gq)
 {
-    const int gq = hq % GROUP;
     float lse_max = -INFINITY;
-    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * GROUP + gq));
+    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * stride + gq));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
 
@@ -265,12 +412,12 @@ __device__ __forceinline__ void merge_one_head(const pd_params& p, const GatherO
     float den = 0.f;
     for (int base = s0; base < s1; base += 32) {
         const int s = base + lane;
-        const float w_mine = s < s1 ? exp2f(__ldcg(p.partial_lse + s * GROUP + gq) - lse_max) : 0.f;
+        const float w_mine = s < s1 ? exp2f(__ldcg(p.partial_lse + s * stride + gq) - lse_max) : 0.f;
         const int n = min(32, s1 - base);
         for (int j = 0; j < n; j++) {
             const float w = __shfl_sync(0xffffffffu, w_mine, j);
             const float4 o = __ldcg(reinterpret_cast<const float4*>(
-                p.partial_out + (static_cast<size_t>(base + j) * GROUP + gq) * HEAD_DIM + lane * 4));
+                p.partial_out + (static_cast<size_t>(base + j) * stride + gq) * HEAD_DIM + lane * 4));
             num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
             num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
             den += w;
@@ -288,17 +435,18 @@ __device__ __forceinline__ void merge_one_head(const pd_params& p, const GatherO
 // together: used by the decode kernel's own merge, where the merging warp holds up its CTA's
 // pipeline until it is done.  Up to 32 segments per row in the fast path.
 template<int GROUP>
-__device__ __forceinline__ void merge_item(const pd_params& p, const GatherOut& gp, int b, int kv_head, int s0, int s1, int lane)
+__device__ __forceinline__ void merge_item(const pd_params& p, const GatherOut& gp, int b, int kv_head, int s0, int s1,
+                                           int lane, int stride = GROUP, int first = 0)
 {
     const int n = s1 - s0;
     if (n > 32) {
-        for (int hd = 0; hd < GROUP; hd++) merge_one_head<GROUP>(p, gp, b, kv_head * GROUP + hd, s0, s1, lane);
+        for (int hd = 0; hd < GROUP; hd++) merge_one_head<GROUP>(p, gp, b, kv_head * GROUP + hd, s0, s1, lane, stride, first + hd);
         return;
     }
     float w[GROUP], den[GROUP];
 #pragma unroll
     for (int hd = 0; hd < GROUP; hd++)
-        w[hd] = lane < n ? __ldcg(p.partial_lse + (s0 + lane) * GROUP + hd) : -INFINITY;   // LSE of segment s0 + lane
+        w[hd] = lane < n ? __ldcg(p.partial_lse + (s0 + lane) * stride + first + hd) : -INFINITY;   // LSE of segment s0 + lane
 #pragma unroll
     for (int hd = 0; hd < GROUP; hd++) {
         float mx = w[hd];
@@ -316,7 +464,7 @@ __device__ __forceinline__ void merge_item(const pd_params& p, const GatherOut& 
 #pragma unroll
         for (int hd = 0; hd < GROUP; hd++)
             o[hd] = __ldcg(reinterpret_cast<const float4*>(
-                p.partial_out + (static_cast<size_t>(s0 + j) * GROUP + hd) * HEAD_DIM + lane * 4));
+                p.partial_out + (static_cast<size_t>(s0 + j) * stride + first + hd) * HEAD_DIM + lane * 4));
 #pragma unroll
         for (int hd = 0; hd < GROUP; hd++) {
             const float wj = __shfl_sync(0xffffffffu, w[hd], j);
@@ -430,7 +578,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         // ================= producer warp =================
         const int bt_tokens = 1 << btl;                 // tokens per box
         const int bpt       = S::TILE >> btl;           // boxes per tile
-        const uint32_t box_bytes = static_cast<uint32_t>(bt_tokens) * S::ROW_BYTES;
+        const uint32_t box_bytes = static_cast<uint32_t>(bt_tokens) * S::ROW_BYTES * S::HEADS;
         const uint64_t pol = l2_evict_first_policy();
         const int ps = p.page_size;
         int issued = 0;                                 // tiles issued so far
@@ -450,7 +598,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             if (*abort_flag) return false;
             const int valid = min(S::TILE, sg.w - tile_tok);
             const int nb = (valid + bt_tokens - 1) >> btl;
-            const bool first_tile = tile_tok == sg.z;     // the segment's query rows ride along
+            const bool first_tile = S::HEADS == 1 && tile_tok == sg.z;   // the segment's query rows ride along
             if (lane == 0) {
                 mbar_expect_tx(full_bar(stage), 2u * nb * box_bytes + (first_tile ? S::Q_SLOT_BYTES : 0));
                 if (first_tile)
@@ -461,22 +609,23 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             __syncwarp();
             const uint32_t k_dst = pipe + stage * S::STAGE_BYTES;
             const uint32_t v_dst = k_dst + S::TILE_BYTES;
+            const int head_coord = S::HEADS == 1 ? sg.y : 0;   // a head-fused box spans kv heads 0..7
             auto copy_box = [&](int j, int page) {
                 const int tok_in_page = (tile_tok + (j << btl)) % ps;
                 if (btl_flags & FLAG_NO_L2_HINT) {
                     if constexpr (FP8) {
-                        tma_load_4d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, sg.y, page);
-                        tma_load_4d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, sg.y, page);
+                        tma_load_4d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, head_coord, page);
+                        tma_load_4d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, head_coord, page);
                     } else {
-                        tma_load_5d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page);
-                        tma_load_5d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page);
+                        tma_load_5d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page);
+                        tma_load_5d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page);
                     }
                 } else if constexpr (FP8) {
-                    tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
-                    tma_load_4d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, sg.y, page, pol);
+                    tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, head_coord, page, pol);
+                    tma_load_4d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, head_coord, page, pol);
                 } else {
-                    tma_load_5d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page, pol);
-                    tma_load_5d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, sg.y, page, pol);
+                    tma_load_5d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page, pol);
+                    tma_load_5d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page, pol);
                 }
             };
             if (bpt <= 32) {
@@ -560,6 +709,26 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     for (int seg = seg_begin; alive && seg < seg_end; seg++) {
         const int4 sg = __ldg(segments + seg);
         bool need_q = true;   // Q^T fragments are read from the slot of the segment's first tile
+        if constexpr (S::HEADS > 1) {
+            // head-fused: this warp's kv head is `warp`; its query rows come straight from global memory
+            const bool live = g < GROUP;
+            const __half* qrow = static_cast<const __half*>(p.q)
+                + (static_cast<size_t>(sg.x) * p.num_q_heads + warp * GROUP + (live ? g : 0)) * HEAD_DIM;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                if constexpr (FP8) {
+                    const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
+                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(qrow + db));
+                    qb[ks][0] = live ? v.x : 0u;
+                    qb[ks][1] = live ? v.y : 0u;
+                } else {
+                    const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd));
+                    const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd));
+                    qb[ks][0] = live ? lo : 0u;
+                    qb[ks][1] = live ? hi : 0u;
+                }
+            }
+        }
 #pragma unroll
         for (int mt = 0; mt < 8; mt++) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
         m_run[0] = m_run[1] = -INFINITY;
@@ -569,7 +738,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const int stage = c_stage;
             if (!mbar_wait(full_bar(stage), c_phase)) { if (lane == 0) fail(ST_FULL_TIMEOUT); alive = false; break; }
             if (*abort_flag) { alive = false; break; }
-            if (need_q) {
+            if (need_q && S::HEADS == 1) {
                 // column n = g is query head g of the group (zero when g >= GROUP)
                 need_q = false;
                 const bool live = g < GROUP;
@@ -597,124 +766,14 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 
 #pragma unroll
             for (int gi = 0; gi < C::GROUPS_PER_WARP; gi++) {
-                const int grp_row = (warp * C::GROUPS_PER_WARP + gi) * 16;
+                const int grp_row = S::HEADS > 1 ? 0 : (warp * C::GROUPS_PER_WARP + gi) * 16;
                 if (grp_row >= valid || no_math) break;           // warp-uniform
                 const int grp_valid = valid - grp_row;            // >= 1; < 16 only in a sequence's last group
+                const int box_head = S::HEADS > 1 ? warp : 0;
 
-                if (grp_valid < 16) {
-                    // Rows past the end hold whatever the page or the stage held before; a NaN
-                    // there would survive P = 0 in the PV product, so clear V's dead rows.
-                    constexpr int CH = S::ROW_BYTES / 16;
-                    for (int idx = lane; idx < 16 * CH; idx += 32) {
-                        const int r = idx / CH, c = idx % CH;
-                        if (r >= grp_valid)
-                            sts128_zero(v_tile + row_offset<KV>(grp_row + r, FP8 ? 0 : (c >> 3), btl) + ((c & 7) << 4));
-                    }
-                    wrote = true;
-                    __syncwarp();
-                }
-
-                // ---- 1. S^T = K Q^T : 16 tokens x 8 heads, two interleaved accumulators.
-                float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-                if constexpr (!FP8) {
-                    const int t = grp_row + (lane & 7) + ((lane >> 3) & 1) * 8;
-                    const uint32_t r0 = row_offset<KV>(t, 0, btl), r1 = row_offset<KV>(t, 1, btl);
-                    const int hi = lane >> 4;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
-                        uint32_t a[4];
-                        ldmatrix_x4(a, k_tile + swz(ks < 4 ? r0 : r1, (ks & 3) * 2 + hi));
-                        if (ks & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
-                        else        mma_16816(s0, a, qb[ks][0], qb[ks][1]);
-                    }
-                } else {
-                    const uint32_t r0 = row_offset<KV>(grp_row + g, 0, btl), r1 = row_offset<KV>(grp_row + g + 8, 0, btl);
-#pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        const uint4 lo = lds128(k_tile + swz(r0, 2 * qd + j));
-                        const uint4 hi = lds128(k_tile + swz(r1, 2 * qd + j));
-                        const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-                        for (int m = 0; m < 4; m++) {
-                            const uint32_t a[4] = {fp8x2_to_half2(wl[m] & 0xffffu), fp8x2_to_half2(wh[m] & 0xffffu),
-                                                   fp8x2_to_half2(wl[m] >> 16),     fp8x2_to_half2(wh[m] >> 16)};
-                            const int ks = 4 * j + m;
-                            if (m & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
-                            else       mma_16816(s0, a, qb[ks][0], qb[ks][1]);
-                        }
-                    }
-                }
-
-                // ---- 2. online softmax. This lane: tokens g, g+8 of the group, heads 2qd, 2qd+1.
-                float x[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) x[i] = (s0[i] + s1[i]) * qk_scale;
-                if (grp_valid < 16) {
-                    if (g >= grp_valid)     { x[0] = -INFINITY; x[1] = -INFINITY; }
-                    if (g + 8 >= grp_valid) { x[2] = -INFINITY; x[3] = -INFINITY; }
-                }
-                float mx[2] = {fmaxf(x[0], x[2]), fmaxf(x[1], x[3])};
-#pragma unroll
-                for (int o = 4; o < 32; o <<= 1) {
-                    mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-                    mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-                }
-                float alpha[2];
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const float m_new = fmaxf(m_run[h], mx[h]);
-                    alpha[h] = exp2f(m_run[h] - m_new);
-                    m_run[h] = m_new;
-                }
-                float pr[4];
-#pragma unroll
-                for (int i = 0; i < 4; i++) pr[i] = exp2f(x[i] - m_run[i & 1]);
-                l_run[0] = l_run[0] * alpha[0] + (pr[0] + pr[2]);
-                l_run[1] = l_run[1] * alpha[1] + (pr[1] + pr[3]);
-#pragma unroll
-                for (int mt = 0; mt < 8; mt++) {
-                    acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
-                    acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
-                }
-
-                // ---- 3. O^T += V^T P^T.  P^T's B fragment = transposed 8x8 blocks of the scores.
-                const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));   // tokens 0..7
-                const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));   // tokens 8..15
-                if constexpr (!FP8) {
-                    const int t = grp_row + (lane & 7) + ((lane >> 4) & 1) * 8;
-                    const uint32_t r0 = row_offset<KV>(t, 0, btl), r1 = row_offset<KV>(t, 1, btl);
-                    const int hi = (lane >> 3) & 1;
-#pragma unroll
-                    for (int mt = 0; mt < 8; mt++) {
-                        uint32_t a[4];
-                        ldmatrix_x4_trans(a, v_tile + swz(mt < 4 ? r0 : r1, (mt & 3) * 2 + hi));
-                        mma_16816(acc[mt], a, pb0, pb1);
-                    }
-                } else {
-                    // This lane: tokens 2qd, 2qd+1, 2qd+8, 2qd+9, dims 16g..16g+15.  M-tile mt has
-                    // row g = dim 16g + 2mt and row g+8 = dim 16g + 2mt + 1.
-                    uint32_t vw[4][4];
-#pragma unroll
-                    for (int r = 0; r < 4; r++) {
-                        const int t = grp_row + 2 * qd + (r & 1) + (r >> 1) * 8;
-                        const uint4 v = lds128(v_tile + swz(row_offset<KV>(t, 0, btl), g));
-                        vw[r][0] = v.x; vw[r][1] = v.y; vw[r][2] = v.z; vw[r][3] = v.w;
-                    }
-#pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        // bytes [t0 d, t1 d, t0 d+1, t1 d+1] for d = 4w (lo) and 4w+2 (hi)
-                        const uint32_t lo01 = __byte_perm(vw[0][w], vw[1][w], 0x5140u);
-                        const uint32_t hi01 = __byte_perm(vw[0][w], vw[1][w], 0x7362u);
-                        const uint32_t lo23 = __byte_perm(vw[2][w], vw[3][w], 0x5140u);
-                        const uint32_t hi23 = __byte_perm(vw[2][w], vw[3][w], 0x7362u);
-                        const uint32_t a_lo[4] = {fp8x2_to_half2(lo01 & 0xffffu), fp8x2_to_half2(lo01 >> 16),
-                                                  fp8x2_to_half2(lo23 & 0xffffu), fp8x2_to_half2(lo23 >> 16)};
-                        const uint32_t a_hi[4] = {fp8x2_to_half2(hi01 & 0xffffu), fp8x2_to_half2(hi01 >> 16),
-                                                  fp8x2_to_half2(hi23 & 0xffffu), fp8x2_to_half2(hi23 >> 16)};
-                        mma_16816(acc[2 * w],     a_lo, pb0, pb1);
-                        mma_16816(acc[2 * w + 1], a_hi, pb0, pb1);
-                    }
-                }
+                wrote |= process_group<KV>(k_tile, v_tile,
+                                           [&](int t, int panel) { return row_offset<KV, S::HEADS>(t, panel, btl, box_head); },
+                                           grp_row, grp_valid, qb, acc, m_run, l_run, qk_scale, lane);
             }
 
             // Release the stage to the producer.
@@ -732,6 +791,54 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             for (int o = 4; o < 32; o <<= 1) {
                 l[0] += __shfl_xor_sync(0xffffffffu, l[0], o);
                 l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
+            }
+            if constexpr (S::HEADS > 1) {
+                // Head-fused: this warp owns kv head `warp` of row sg.x outright.  Work items are rows:
+                // item_seg_begin is indexed by row, partials by (segment, query head).  Every lane
+                // normalises and stores its own fragment values; nothing is exchanged between warps.
+                const int s0 = p.item_seg_begin[sg.x], s1 = p.item_seg_begin[sg.x + 1];
+                const bool whole_row = s1 - s0 == 1;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int hd = 2 * qd + h;
+                    if (hd < GROUP) {
+                        const int hq = warp * GROUP + hd;
+                        const float inv = p.v_scale / l[h];
+                        const size_t prow = (static_cast<size_t>(seg) * p.num_q_heads + hq) * HEAD_DIM;
+                        const size_t orow = out_index(p, gp, sg.x, hq);
+#pragma unroll
+                        for (int mt = 0; mt < 8; mt++) {
+                            const int d0 = FP8 ? 16 * g + 2 * mt : 16 * mt + g;
+                            const int d1 = FP8 ? d0 + 1 : d0 + 8;
+                            const float o0 = acc[mt][h] * inv, o1 = acc[mt][2 + h] * inv;
+                            if (whole_row) {
+                                store_out(p, gp, orow + d0, __float2half(o0));
+                                store_out(p, gp, orow + d1, __float2half(o1));
+                            } else {
+                                p.partial_out[prow + d0] = o0;
+                                p.partial_out[prow + d1] = o1;
+                            }
+                        }
+                        if (!whole_row && g == 0)
+                            p.partial_lse[static_cast<size_t>(seg) * p.num_q_heads + hq] = m_run[h] + log2f(l[h]);
+                    }
+                }
+                if (!whole_row && p.needs_merge == MERGE_IN_KERNEL) {
+                    // one arrival counter per (row, kv head); the warp that completes it merges the head's group
+                    int* counter = reinterpret_cast<int*>(p.partial_lse + static_cast<size_t>(p.cta_seg_begin[p.num_ctas]) * p.num_q_heads)
+                                   + sg.x * S::HEADS + warp;
+                    __threadfence();
+                    __syncwarp();
+                    int seen = 0;
+                    if (lane == 0) seen = atomicAdd(counter, 1);
+                    seen = __shfl_sync(0xffffffffu, seen, 0);
+                    if (seen == s1 - s0 - 1) {
+                        __threadfence();
+                        merge_item<GROUP>(p, gp, sg.x, warp, s0, s1, lane, p.num_q_heads, warp * GROUP);
+                        if (lane == 0) *counter = 0;
+                    }
+                }
+                continue;
             }
             const int item = sg.x * p.num_kv_heads + sg.y;
             const bool whole = p.item_seg_begin[item + 1] - p.item_seg_begin[item] == 1;
@@ -815,7 +922,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 // then over the head dimension, four floats per lane, with each segment's weight
 // broadcast by shuffle.  Same arithmetic as merge_segments_kernel
 // (src/decode/decode_kernels.cuh:409-432).
-template<int GROUP>
+// ROW_ITEMS = true: the plan's work items are rows (head-fused tiles).
+template<int GROUP, bool ROW_ITEMS = false>
 __global__ void __launch_bounds__(128)
 merge_segments_kernel(const __grid_constant__ pd_params p)
 {
@@ -823,11 +931,12 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     const int idx  = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (row, q head)
     if (idx >= p.batch * p.num_q_heads) return;
     const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
-    const int item = b * p.num_kv_heads + hq / GROUP;
+    const int item = ROW_ITEMS ? b : b * p.num_kv_heads + hq / GROUP;
     const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
     GatherOut local{};   // world = 0: plain output
-    merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane);
+    if (ROW_ITEMS) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, p.num_q_heads, hq);
+    else           merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, GROUP, hq % GROUP);
 }
 
 // Waits (bounded) until every peer's flag has reached `epoch`: their slices are in this GPU's

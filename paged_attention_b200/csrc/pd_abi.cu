@@ -23,6 +23,7 @@
 #include <numeric>
 #include <random>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 namespace {
@@ -112,6 +113,45 @@ const KernelInfo* info_by_group(int group) {
     }
     return nullptr;
 }
+
+// Head-fused tiles (all 8 kv heads of 16 tokens per tile, one consumer warp per kv head); used for
+// fp16 plans made by pd_make_plan when the layer has exactly 8 kv heads: 3 stages of 64 KB, one CTA per
+// SM.  Measured on the batch 64 x 8192 layer: 314 us against 320 us for the (row, kv head) schedule, and
+// 0.9 % instead of 2.6 % over one contiguous page per sequence.  The fp8 cache gains nothing from it
+// (170 us either way at one or two CTAs per SM: the fp8 path is bound by its widening arithmetic, not by
+// DRAM locality), so fp8 keeps the (row, kv head) schedule at three CTAs per SM.
+template<typename KV> struct FusedConfig;
+template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>; };
+
+template<int GROUP>
+void launch_merge_rows(const pd_params& p, cudaStream_t stream) {
+    const int rows = p.batch * p.num_q_heads;
+    pdk::merge_segments_kernel<GROUP, true><<<(rows + 3) / 4, 128, 0, stream>>>(p);
+}
+
+template<typename KV, int GROUP>
+KernelInfo make_fused_info() {
+    using C = typename FusedConfig<KV>::type;
+    using S = pdk::Shape<KV, GROUP, C>;
+    return KernelInfo{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
+                      S::SMEM_BYTES, C::MIN_CTAS, &launch_decode<KV, GROUP, C>, &launch_merge_rows<GROUP>};
+}
+
+template<typename KV>
+const KernelInfo* fused_info(int group) {
+    static const KernelInfo t[4] = {make_fused_info<KV, 1>(), make_fused_info<KV, 2>(), make_fused_info<KV, 4>(),
+                                    make_fused_info<KV, 8>()};
+    switch (group) {
+        case 1: return &t[0];
+        case 2: return &t[1];
+        case 4: return &t[2];
+        case 8: return &t[3];
+    }
+    return nullptr;
+}
+constexpr int FUSED_HEADS = 8;
+constexpr int FUSED_TILE  = 16;
+bool g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr;
 
 template<typename KV>
 const KernelInfo* info_by_variant(int variant, int group) {
@@ -207,7 +247,7 @@ unsigned gcd_u(unsigned a, unsigned b) { while (b) { const unsigned t = a % b; a
 //   fp8 : 4-D  (128 dims, token, kv head, page),       box (128, 2^btl, 1, 1)
 // so a box lands in shared memory as [panel][token][128 bytes] under the 128-byte swizzle.
 int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages, int num_kv_heads,
-                    int page_size, int btl) {
+                    int page_size, int btl, int box_heads = 1) {
     EncodeTiledFn enc;
     if (int rc = encode_fn(&enc)) return rc;
     if (reinterpret_cast<uintptr_t>(pool) % 16 != 0)
@@ -223,7 +263,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
     if (dtype == PD_FP16) {
         const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
         const cuuint64_t strides[4] = {row, 128, row * page_size, row * page_size * num_kv_heads};
-        const cuuint32_t box[5]     = {64, 1u << btl, 2, 1, 1};
+        const cuuint32_t box[5]     = {64, 1u << btl, 2, static_cast<cuuint32_t>(box_heads), 1};
         const cuuint32_t estr[5]    = {1, 1, 1, 1, 1};
         r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(pool), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
@@ -231,7 +271,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
     } else {
         const cuuint64_t dims[4]    = {128, static_cast<cuuint64_t>(page_size), static_cast<cuuint64_t>(num_kv_heads), pages};
         const cuuint64_t strides[3] = {row, row * page_size, row * page_size * num_kv_heads};
-        const cuuint32_t box[4]     = {128, 1u << btl, 1, 1};
+        const cuuint32_t box[4]     = {128, 1u << btl, static_cast<cuuint32_t>(box_heads), 1};
         const cuuint32_t estr[4]    = {1, 1, 1, 1};
         r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(pool), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
@@ -259,6 +299,10 @@ struct pd_plan {
     std::vector<int> segments;        // 4 ints each
     std::vector<int> cta_seg_begin;
     std::vector<int> item_seg_begin;
+    // what pd_make_plan knew when it cut the plan (dtype < 0: unknown, e.g. built from arrays); lets the
+    // device plan also carry the head-fused schedule of the same step
+    int dtype = -1, batch = 0, num_q_heads = 0, num_kv_heads = 0, forced_ctas = 0;
+    std::vector<int> seq_lens;
 };
 
 namespace {
@@ -354,7 +398,23 @@ struct pd_device_plan {
     int    num_ctas = 0;
     int    needs_merge = 0;
     int    num_segments = 0;
+    int    num_items = 0;
+    struct Fused {                 // the same step cut into head-fused row segments (valid: exactly 8 kv heads)
+        bool valid = false;
+        int dtype = -1, group = 0, batch = 0, num_ctas = 0, num_segments = 0, needs_merge = 0;
+        size_t rows = 0;           // segments * num_q_heads
+        const void* segments = nullptr;
+        const int* cta_seg_begin = nullptr;
+        const int* row_seg_begin = nullptr;
+        float* partial_out = nullptr;
+    } fused;
 };
+
+namespace {
+// Launch-time lookup: standard segment array (what pd_params carries) -> head-fused schedule.
+std::mutex g_fused_mutex;
+std::unordered_map<const void*, pd_device_plan::Fused> g_fused_registry;
+}  // namespace
 
 // ---- cache -----------------------------------------------------------------------------------------
 
@@ -388,6 +448,12 @@ const char* pd_version(void) { return "pd_b200 0.1 (sm_100a)"; }
 
 int pd_kv_dtype_bytes(int dtype) { return dtype == PD_FP16 ? 2 : 1; }
 const char* pd_kv_dtype_name(int dtype) { return dtype == PD_FP16 ? "fp16" : "fp8_e4m3"; }
+
+int pd_set_head_fused(int on) {
+    g_head_fused = on != 0;
+    return PD_OK;
+}
+int pd_head_fused(void) { return g_head_fused ? 1 : 0; }
 
 int pd_set_kernel_variant(int variant) {
     if (variant < 0 || variant >= NUM_VARIANTS) return set_error(PD_INVALID_ARGUMENT, "kernel variant %d does not exist", variant);
@@ -444,9 +510,15 @@ int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int
     const int group = num_q_heads / num_kv_heads;
     int tile = 0;
     if (int rc = pd_tile_tokens(dtype, head_dim, group, &tile)) return rc;
+    const int forced = num_ctas > 0 ? num_ctas : 0;
     if (num_ctas <= 0)
         if (int rc = pd_default_ctas(dtype, head_dim, group, &num_ctas)) return rc;
-    return build_plan(tile, seq_lens, batch, num_q_heads, num_kv_heads, num_ctas, out);
+    if (int rc = build_plan(tile, seq_lens, batch, num_q_heads, num_kv_heads, num_ctas, out)) return rc;
+    pd_plan* plan = *out;
+    plan->dtype = dtype; plan->batch = batch; plan->num_q_heads = num_q_heads; plan->num_kv_heads = num_kv_heads;
+    plan->forced_ctas = forced;
+    plan->seq_lens.assign(seq_lens, seq_lens + batch);
+    return PD_OK;
 }
 
 int pd_plan_from_arrays(int num_ctas, int tile, const int* segments, int num_segments, const int* cta_seg_begin,
@@ -497,6 +569,10 @@ int pd_device_plan_create(pd_device_plan** out) {
 
 void pd_device_plan_destroy(pd_device_plan* dp) {
     if (!dp) return;
+    if (dp->segments) {
+        std::lock_guard<std::mutex> lock(g_fused_mutex);
+        g_fused_registry.erase(dp->segments);
+    }
     if (dp->staged) { cudaEventSynchronize(dp->staged); cudaEventDestroy(dp->staged); }
     cudaFree(dp->arena);
     cudaFree(dp->partial);
@@ -510,10 +586,37 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     const size_t nseg = plan->segments.size() / 4;
     auto round16 = [](size_t x) { return (x + 15) & ~static_cast<size_t>(15); };
+
+    // The same step as head-fused row segments, when the plan says enough about the layer (made by
+    // pd_make_plan) and the layer has exactly 8 kv heads: rows are the work items, 16 tokens the unit.
+    pd_plan* rows_plan = nullptr;
+    const KernelInfo* fk = nullptr;
+    if (plan->dtype == PD_FP16 && plan->num_kv_heads == FUSED_HEADS && plan->batch > 0 && plan->num_q_heads / plan->num_kv_heads == group &&
+        head_dim == 128) {
+        fk = fused_info<__half>(group);
+        int grid = plan->forced_ctas;
+        if (fk && grid <= 0) {
+            int dev = 0, sms = 0, resident = 0;
+            if (configure(fk) == PD_OK && cudaGetDevice(&dev) == cudaSuccess &&
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fk->fn, fk->threads, fk->smem) == cudaSuccess)
+                grid = sms * std::min(resident, fk->per_sm);
+        }
+        if (!fk || grid <= 0 ||
+            build_plan(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
+            rows_plan = nullptr;
+    }
+    struct PlanGuard { pd_plan* p; ~PlanGuard() { delete p; } } guard{rows_plan};
+
     const size_t seg_bytes  = round16(sizeof(int) * plan->segments.size());
     const size_t cta_bytes  = round16(sizeof(int) * plan->cta_seg_begin.size());
     const size_t item_bytes = round16(sizeof(int) * plan->item_seg_begin.size());
-    const size_t total = seg_bytes + cta_bytes + item_bytes;
+    const size_t std_bytes  = seg_bytes + cta_bytes + item_bytes;
+    const size_t fseg_bytes = rows_plan ? round16(sizeof(int) * rows_plan->segments.size()) : 0;
+    const size_t fcta_bytes = rows_plan ? round16(sizeof(int) * rows_plan->cta_seg_begin.size()) : 0;
+    const size_t frow_bytes = rows_plan ? round16(sizeof(int) * rows_plan->item_seg_begin.size()) : 0;
+    const size_t total = std_bytes + fseg_bytes + fcta_bytes + frow_bytes;
+    const void* old_key = dp->segments;
     if (total > dp->arena_cap) {
         PD_CUDA(cudaFree(dp->arena));
         dp->arena = nullptr; dp->arena_cap = 0;
@@ -532,14 +635,23 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     std::memcpy(h, plan->segments.data(), sizeof(int) * plan->segments.size());
     std::memcpy(h + seg_bytes, plan->cta_seg_begin.data(), sizeof(int) * plan->cta_seg_begin.size());
     std::memcpy(h + seg_bytes + cta_bytes, plan->item_seg_begin.data(), sizeof(int) * plan->item_seg_begin.size());
+    if (rows_plan) {
+        std::memcpy(h + std_bytes, rows_plan->segments.data(), sizeof(int) * rows_plan->segments.size());
+        std::memcpy(h + std_bytes + fseg_bytes, rows_plan->cta_seg_begin.data(), sizeof(int) * rows_plan->cta_seg_begin.size());
+        std::memcpy(h + std_bytes + fseg_bytes + fcta_bytes, rows_plan->item_seg_begin.data(),
+                    sizeof(int) * rows_plan->item_seg_begin.size());
+    }
     if (total) PD_CUDA(cudaMemcpyAsync(dp->arena, dp->staging, total, cudaMemcpyHostToDevice, stream));
     PD_CUDA(cudaEventRecord(dp->staged, stream));
 
-    // Workspace for split rows: [segments][group][head_dim] outputs, [segments][group] LSEs, then
-    // one arrival counter per (row, kv head) for the in-kernel merge (zero between launches: the
-    // merging warp re-arms its counter).
+    // Workspace for split rows, one region per schedule: [segments][heads][head_dim] outputs,
+    // [segments][heads] LSEs, then one arrival counter per (row, kv head) for the in-kernel merge (zero
+    // between launches: the merging warp re-arms its counter).
     const size_t rows = nseg * group;
-    const size_t need = rows * (head_dim + 1) + plan->num_items;
+    const size_t std_need = rows * (head_dim + 1) + plan->num_items;
+    const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * plan->num_q_heads : 0;
+    const size_t f_need = rows_plan ? frows * (head_dim + 1) + plan->num_items : 0;
+    const size_t need = std_need + f_need;
     if (need > dp->partial_cap) {
         PD_CUDA(cudaFree(dp->partial));
         dp->partial = nullptr; dp->partial_cap = 0;
@@ -554,18 +666,43 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     dp->partial_lse    = dp->partial ? dp->partial + rows * head_dim : nullptr;
     dp->num_ctas       = plan->num_ctas;
     dp->num_segments   = static_cast<int>(nseg);
-    dp->needs_merge    = static_cast<int>(nseg) > plan->num_items ? pdk::MERGE_IN_KERNEL : 0;
-    // The in-kernel merge is done by ONE warp per split row; that is the cheaper way while rows are
-    // cut in a few pieces (a long batch: 2-3 segments per row), but a row cut in dozens of pieces
-    // (one long sequence spread over the whole grid) merges faster in the separate kernel, which
-    // puts a warp on every (row, query head).
-    int widest = 0;
-    for (int i = 0; i < plan->num_items; i++)
-        widest = std::max(widest, plan->item_seg_begin[i + 1] - plan->item_seg_begin[i]);
+    dp->num_items      = plan->num_items;
+    // Where rows are cut in a few pieces (a long batch: 2-3 segments per row) the decode kernel merges
+    // them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
+    // the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
     static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
-    if (dp->needs_merge && (separate_merge || widest > 4)) dp->needs_merge = pdk::MERGE_SEPARATE;
-    if (dp->needs_merge && plan->num_items)
+    auto merge_mode = [&](const pd_plan& pl) {
+        const int items = static_cast<int>(pl.item_seg_begin.size()) - 1;
+        if (static_cast<int>(pl.segments.size() / 4) <= items) return 0;
+        int widest = 0;
+        for (int i = 0; i < items; i++) widest = std::max(widest, pl.item_seg_begin[i + 1] - pl.item_seg_begin[i]);
+        return (separate_merge || widest > 4) ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
+    };
+    dp->needs_merge = merge_mode(*plan);
+    if (plan->num_items)
         PD_CUDA(cudaMemsetAsync(dp->partial + rows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
+
+    dp->fused = pd_device_plan::Fused{};
+    if (rows_plan) {
+        auto& f = dp->fused;
+        f.valid = true;
+        f.dtype = plan->dtype; f.group = group; f.batch = plan->batch;
+        f.num_ctas = rows_plan->num_ctas;
+        f.num_segments = static_cast<int>(rows_plan->segments.size() / 4);
+        f.needs_merge = merge_mode(*rows_plan);
+        f.rows = frows;
+        f.segments = a + std_bytes;
+        f.cta_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes);
+        f.row_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes + fcta_bytes);
+        f.partial_out = dp->partial + std_need;
+        PD_CUDA(cudaMemsetAsync(f.partial_out + frows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_fused_mutex);
+        if (old_key) g_fused_registry.erase(old_key);
+        if (dp->fused.valid) g_fused_registry[dp->segments] = dp->fused;
+        else g_fused_registry.erase(dp->segments);
+    }
     return PD_OK;
 }
 
@@ -601,6 +738,42 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: split rows need the partial workspace");
     if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0)
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: q must be 16-byte aligned");
+    // Head-fused schedule: taken when the plan these params were bound to carries one (see
+    // pd_device_plan_upload), i.e. the layer has 8 kv heads and the plan came from pd_make_plan.
+    // needs_merge < 0 (diagnostic): run the decode kernel only and leave split rows unmerged.
+    pd_params fused_params;
+    pd_params unmerged;
+    if (p->needs_merge < 0) {
+        unmerged = *p;
+        unmerged.needs_merge = 0;
+    }
+    const bool skip_merge = p->needs_merge < 0;
+    int box_heads = 1;
+    if (g_head_fused && p->num_kv_heads == FUSED_HEADS) {
+        pd_device_plan::Fused f;
+        bool found = false;
+        {
+            std::lock_guard<std::mutex> lock(g_fused_mutex);
+            auto it = g_fused_registry.find(p->segments);
+            if (it != g_fused_registry.end()) { f = it->second; found = true; }
+        }
+        const KernelInfo* fk = dtype == PD_FP16 ? fused_info<__half>(p->num_q_heads / p->num_kv_heads) : nullptr;
+        if (found && fk && f.dtype == dtype && f.batch == p->batch && f.group == p->num_q_heads / p->num_kv_heads) {
+            fused_params = *p;
+            fused_params.segments = f.segments;
+            fused_params.cta_seg_begin = f.cta_seg_begin;
+            fused_params.item_seg_begin = f.row_seg_begin;       // work items are rows
+            fused_params.num_ctas = f.num_ctas;
+            fused_params.needs_merge = p->needs_merge < 0 ? 0 : f.needs_merge;   // the row schedule has its own splits
+            if (gather.world && fused_params.needs_merge) fused_params.needs_merge = pdk::MERGE_IN_KERNEL;   // gathered rows are written by the decode kernel
+            fused_params.partial_out = f.partial_out;
+            fused_params.partial_lse = f.partial_out + f.rows * p->head_dim;
+            p = &fused_params;
+            k = fk;
+            box_heads = FUSED_HEADS;
+        }
+    }
+    if (skip_merge && box_heads == 1) p = &unmerged;
     if (int rc = configure(k)) return rc;
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -610,8 +783,8 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     int btl = 0;
     while ((1u << (btl + 1)) <= box_tokens) btl++;
     CUtensorMap k_map, v_map;
-    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
-    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads)) return rc;
+    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     static const bool load_only = std::getenv("PD_B200_LOAD_ONLY") != nullptr;   // diagnostic, see decode_kernel.cuh

@@ -68,6 +68,15 @@ def kernel_variant():
     return _lib.lib().pd_kernel_variant()
 
 
+def set_head_fused(on):
+    """Switch the head-fused schedule (layers with 8 kv heads) on or off; re-plan afterwards."""
+    check(_lib.lib().pd_set_head_fused(int(bool(on))))
+
+
+def head_fused():
+    return bool(_lib.lib().pd_head_fused())
+
+
 class DecodePlan:
     """decode::DecodePlan (src/decode/decode.hpp:21-27). Owns (or borrows) a pd_plan handle."""
 
@@ -307,4 +316,4 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant"]
+           "make_plan_tiled", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused"]

@@ -42,7 +42,23 @@ def _problem(torch, pa, dtype, lens, num_ctas, seed):
 @pytest.mark.parametrize("dtype", [0, 1])
 def test_static_workspace_decode_matches_allocating_decode(dtype, torch_cuda, pa):
     torch = torch_cuda
+    # The new entry point always runs the (row, kv head) schedule, so compare it with the existing entry
+    # point on that same schedule (bit for bit), and with the default head-fused schedule within TOL.
+    fused_before = pa.head_fused()
     cache, cfg, dplan, plan, p, q = _problem(torch, pa, dtype, [3000, 700, 4099, 90], 200, 21)
+    default_out = torch.zeros_like(q)
+    p.out = default_out.data_ptr()
+    pa.paged_decode(pa.KVDtype(dtype), p, 0, cfg.num_pages)
+    torch.cuda.synchronize()
+    pa.set_head_fused(False)
+    try:
+        _check_static_against_existing(torch, pa, dtype, cache, cfg, dplan, plan, p, q, default_out)
+    finally:
+        pa.set_head_fused(fused_before)
+    cache.close()
+
+
+def _check_static_against_existing(torch, pa, dtype, cache, cfg, dplan, plan, p, q, default_out):
     want = torch.zeros_like(q)
     p.out = want.data_ptr()
     pa.paged_decode(pa.KVDtype(dtype), p, 0, cfg.num_pages)          # the existing entry point
@@ -59,6 +75,7 @@ def test_static_workspace_decode_matches_allocating_decode(dtype, torch_cuda, pa
         assert torch.isfinite(got).all()
         assert (got.float() - want.float()).abs().max().item() <= TOL, f"call {call}"
         assert torch.equal(got, want), f"call {call}: same kernels, same plan, so the same bits"
+        assert (got.float() - default_out.float()).abs().max().item() <= TOL
 
     # a different, smaller problem right after: whatever the workspace still holds must not matter
     cache2, cfg2, dplan2, plan2, p2, q2 = _problem(torch, pa, dtype, [513, 64, 2000], 77, 5)
@@ -69,7 +86,6 @@ def test_static_workspace_decode_matches_allocating_decode(dtype, torch_cuda, pa
     pa.paged_decode_static(pa.KVDtype(dtype), p2, plan2.num_segments, 0, cfg2.num_pages, None)
     torch.cuda.synchronize()
     assert torch.equal(got2, want2)
-    cache.close()
     cache2.close()
 
 
