@@ -151,7 +151,7 @@ const KernelInfo* fused_info(int group) {
 }
 constexpr int FUSED_HEADS = 8;
 constexpr int FUSED_TILE  = 16;
-bool g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr;
+int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   // 0 never, 1 where it wins, 2 always
 
 template<typename KV>
 const KernelInfo* info_by_variant(int variant, int group) {
@@ -449,11 +449,12 @@ const char* pd_version(void) { return "pd_b200 0.1 (sm_100a)"; }
 int pd_kv_dtype_bytes(int dtype) { return dtype == PD_FP16 ? 2 : 1; }
 const char* pd_kv_dtype_name(int dtype) { return dtype == PD_FP16 ? "fp16" : "fp8_e4m3"; }
 
-int pd_set_head_fused(int on) {
-    g_head_fused = on != 0;
+int pd_set_head_fused(int mode) {
+    if (mode < 0 || mode > 2) return set_error(PD_INVALID_ARGUMENT, "set_head_fused: mode must be 0, 1 or 2");
+    g_head_fused = mode;
     return PD_OK;
 }
-int pd_head_fused(void) { return g_head_fused ? 1 : 0; }
+int pd_head_fused(void) { return g_head_fused; }
 
 int pd_set_kernel_variant(int variant) {
     if (variant < 0 || variant >= NUM_VARIANTS) return set_error(PD_INVALID_ARGUMENT, "kernel variant %d does not exist", variant);
@@ -758,7 +759,9 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
             if (it != g_fused_registry.end()) { f = it->second; found = true; }
         }
         const KernelInfo* fk = dtype == PD_FP16 ? fused_info<__half>(p->num_q_heads / p->num_kv_heads) : nullptr;
-        if (found && fk && f.dtype == dtype && f.batch == p->batch && f.group == p->num_q_heads / p->num_kv_heads) {
+        // Mode 1 keeps the (row, kv head) schedule where rows would be spread over more than 4 CTAs each.
+        const bool wins = g_head_fused == 2 || f.needs_merge != pdk::MERGE_SEPARATE;
+        if (found && fk && wins && f.dtype == dtype && f.batch == p->batch && f.group == p->num_q_heads / p->num_kv_heads) {
             fused_params = *p;
             fused_params.segments = f.segments;
             fused_params.cta_seg_begin = f.cta_seg_begin;

@@ -68,13 +68,15 @@ def kernel_variant():
     return _lib.lib().pd_kernel_variant()
 
 
-def set_head_fused(on):
-    """Switch the head-fused schedule (layers with 8 kv heads) on or off; re-plan afterwards."""
-    check(_lib.lib().pd_set_head_fused(int(bool(on))))
+def set_head_fused(mode):
+    """Head-fused schedule of fp16 layers with 8 kv heads: 0 / False never, 1 / True where it wins
+    (the default), 2 whenever the layer allows it."""
+    check(_lib.lib().pd_set_head_fused(int(mode)))
 
 
 def head_fused():
-    return bool(_lib.lib().pd_head_fused())
+    """The current mode: 0, 1 or 2."""
+    return int(_lib.lib().pd_head_fused())
 
 
 class DecodePlan:

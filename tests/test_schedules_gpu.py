@@ -1,8 +1,8 @@
 """The two schedules of the fp16 decode kernel on layers with 8 kv heads.
 
 Plans made by the planner run, by default, with tiles of 16 tokens x all 8 kv heads (one consumer warp
-per kv head, work cut by rows); with the switch off they run the (row, kv head) schedule that every
-other shape uses.  Both must agree with the oracle within the path's tolerance and with each other,
+per kv head, work cut by rows) where that wins (rows cut in at most 4 pieces); otherwise, and with the
+switch off, they run the (row, kv head) schedule that every other shape uses.  The tests force each.  Both must agree with the oracle within the path's tolerance and with each other,
 also when rows are cut into many pieces (separate merge kernel), for ragged batches, odd page sizes,
 indirect slots and appends between steps.
 """
@@ -23,9 +23,9 @@ def both_schedules(pa):
     def run(fn):
         outs = []
         try:
-            for fused in (True, False):
-                pa.set_head_fused(fused)
-                assert pa.head_fused() == fused
+            for mode in (2, 0):          # always head-fused, never head-fused
+                pa.set_head_fused(mode)
+                assert pa.head_fused() == mode
                 outs.append(fn())
         finally:
             pa.set_head_fused(before)
