@@ -41,6 +41,7 @@ WORKLOADS = {
     "c2-onepage": (0, 64, 8192, 32, 8, 8192, "c2 with one contiguous 8192-token page per sequence"),
     "small": (0, 8, 8192, 32, 8, 16, "profiling case: batch 8 x 8192 fp16 (268 MB of KV, larger than L2)"),
     "small-fp8": (1, 16, 8192, 32, 8, 16, "profiling case: batch 16 x 8192 fp8 (268 MB of KV)"),
+    "small-wide": (0, 64, 1024, 32, 8, 16, "profiling case of the head-fused schedule: batch 64 x 1024 fp16 (268 MB of KV)"),
 }
 
 
