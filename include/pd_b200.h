@@ -154,6 +154,27 @@ void pd_device_plan_destroy(pd_device_plan* dp);
 int  pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, int head_dim, void* stream);
 int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
 
+/* Device-side planner.  No counterpart in the reference, whose plan is always cut on the host from host
+ * lengths (src/decode/decode.cu:65-108) and copied over (decode.cu:112-156); its README lists a
+ * device-side, graph-capturable planner as future work.  pd_device_plan_build cuts the same plan with one
+ * small kernel from lengths that already live on the device (row b has seq_lens[slot_ids ? slot_ids[b] : b]):
+ * the segment, CTA and item arrays it leaves in the device plan are bit-identical to pd_make_plan's for
+ * the same lengths and grid.  The call never waits for the device and copies nothing from the host; its
+ * buffers only grow (sized for batch * num_kv_heads + grid segments), so once it has run with the
+ * largest batch it allocates nothing and may be captured into a CUDA graph together with the decode that
+ * follows.  num_ctas <= 0: pd_default_ctas.  The launch grid is num_ctas; CTAs the cut does not need idle.
+ * pd_device_plan_bind then sets needs_merge = 3: rows cut in at most 4 pieces are merged inside the decode
+ * kernel, the others by the merge kernel, which is always launched (the host cannot know).  Rows are
+ * always scheduled by (row, kv head).  A length <= 0 gives that row no work and is reported by
+ * pd_device_plan_info (the host planner refuses such a batch).
+ * pd_device_plan_info (waits for the stream): out[0] CTAs with work, out[1] segments, out[2] most pieces
+ * any (row, kv head) was cut in, out[3] 1 + first row with a length <= 0 (0: none).
+ * pd_device_plan_fetch (waits for the stream): the plan as a host object, for inspection and tests. */
+int  pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, const int* d_slot_ids, int batch,
+                          int num_q_heads, int num_kv_heads, int head_dim, int num_ctas, void* stream);
+int  pd_device_plan_info(const pd_device_plan* dp, int* out, void* stream);
+int  pd_device_plan_fetch(const pd_device_plan* dp, pd_plan** out, void* stream);
+
 /* decode::paged_decode (src/decode/decode.hpp:66): the split kernel and, if any
  * (row, head) was split across CTAs, the merge.  head_dim 128; group 1, 2, 4, 8.
  * num_pages > 0 bounds the page coordinate of the TMA descriptors (page ids
@@ -260,6 +281,11 @@ int    pd_cache_append_batch(pd_cache* c, int count, const int* slots, const voi
 int    pd_cache_release(pd_cache* c, int slot);
 void   pd_cache_shuffle_free_pages(pd_cache* c, unsigned seed);
 int    pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads, int num_ctas, void* stream);
+/* plan() through the device-side planner (pd_device_plan_build) from the cache's own device lengths, which
+ * appends update in stream order.  d_slot_ids: device array of `batch` slot numbers that stays valid until
+ * the last run() of this plan, or NULL for slots 0..batch-1.  pd_cache_last_plan returns NULL afterwards.
+ * No counterpart in the reference. */
+int    pd_cache_plan_device(pd_cache* c, const int* d_slot_ids, int batch, int num_q_heads, int num_ctas, void* stream);
 int    pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream);
 int    pd_cache_decode(pd_cache* c, const void* d_q, void* d_out, int batch, int num_q_heads,
                        int num_ctas, void* stream);

@@ -80,6 +80,9 @@ SIGNATURES = {
     "pd_device_plan_destroy": (None, [_vp]),
     "pd_device_plan_upload": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp]),
     "pd_device_plan_bind": (C.c_int, [_vp, C.POINTER(pd_params)]),
+    "pd_device_plan_build": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "pd_device_plan_info": (C.c_int, [_vp, _i32p, _vp]),
+    "pd_device_plan_fetch": (C.c_int, [_vp, C.POINTER(_vp), _vp]),
     "pd_paged_decode": (C.c_int, [C.c_int, C.POINTER(pd_params), _vp]),
     "pd_paged_decode_bounded": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp]),
     "pd_paged_decode_static": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, C.c_int, _vp, _vp]),
@@ -108,6 +111,7 @@ SIGNATURES = {
     "pd_cache_release": (C.c_int, [_vp, C.c_int]),
     "pd_cache_shuffle_free_pages": (None, [_vp, C.c_uint]),
     "pd_cache_plan": (C.c_int, [_vp, _i32p, C.c_int, C.c_int, C.c_int, _vp]),
+    "pd_cache_plan_device": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_cache_run": (C.c_int, [_vp, _vp, _vp, _vp]),
     "pd_cache_decode": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_cache_last_plan": (_vp, [_vp]),

@@ -48,6 +48,11 @@ constexpr int FLAG_NO_L2_HINT = 0x200;
 // itself; the workspace then carries one zeroed int per (row, kv head) after the LSE array.
 constexpr int MERGE_SEPARATE  = 1;
 constexpr int MERGE_IN_KERNEL = 2;
+// Plans cut on the device: the host cannot know how rows were cut, so each (row, kv head) decides for
+// itself.  Cut in at most HYBRID_MAX_PIECES pieces: merged by the decode kernel's last arriver; in more:
+// left to merge_segments_kernel, which is always launched in this mode and skips everything else.
+constexpr int MERGE_HYBRID = 3;
+constexpr int HYBRID_MAX_PIECES = 4;
 
 constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a tile
 constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
@@ -888,11 +893,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 }
                 if (!consumer_sync()) break;   // scratch is rewritten by the next pass / segment
             }
-            if (alive && !whole && p.needs_merge == MERGE_IN_KERNEL) {
+            const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
+            if (alive && !whole && (p.needs_merge == MERGE_IN_KERNEL ||
+                                    (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES))) {
                 // Last one in merges: every consumer warp of every segment of this (row, kv head)
                 // publishes its partial stores and counts itself; the warp that completes the count
                 // finds all partials visible and combines them, then re-arms the counter.
-                const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
                 int* counter = reinterpret_cast<int*>(p.partial_lse + static_cast<size_t>(p.cta_seg_begin[p.num_ctas]) * GROUP) + item;
                 __threadfence();
                 __syncwarp();
@@ -934,6 +940,7 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     const int item = ROW_ITEMS ? b : b * p.num_kv_heads + hq / GROUP;
     const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
+    if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) return;   // merged by the decode kernel
     GatherOut local{};   // world = 0: plain output
     if (ROW_ITEMS) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, p.num_q_heads, hq);
     else           merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, GROUP, hq % GROUP);

@@ -8,6 +8,7 @@
 
 #include "append_kernel.cuh"
 #include "decode_kernel.cuh"
+#include "plan_kernel.cuh"
 #include "probe_kernel.cuh"
 
 #include <cuda.h>
@@ -399,6 +400,11 @@ struct pd_device_plan {
     int    needs_merge = 0;
     int    num_segments = 0;
     int    num_items = 0;
+    // set by pd_device_plan_build (plan cut on the device): scratch and result slots inside the arena
+    bool   built_on_device = false;
+    int    tile = 0;
+    int*   row_tile_begin = nullptr;
+    int*   info = nullptr;
     struct Fused {                 // the same step cut into head-fused row segments (valid: exactly 8 kv heads)
         bool valid = false;
         int dtype = -1, group = 0, batch = 0, num_ctas = 0, num_segments = 0, needs_merge = 0;
@@ -430,6 +436,8 @@ struct pd_cache {
     pd_device_plan* device_plan = nullptr;
     int plan_batch = 0, plan_num_q_heads = 0;
     bool plan_identity = false;
+    bool plan_on_device = false;          // the current plan was cut by pd_cache_plan_device
+    const int* plan_slot_ids = nullptr;   // ... for these rows (device pointer of the caller, or null)
     std::vector<int> free_pages;
     std::vector<std::vector<int>> tables;
     std::vector<int> seq_lens;
@@ -665,6 +673,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     dp->item_seg_begin = reinterpret_cast<const int*>(a + seg_bytes + cta_bytes);
     dp->partial_out    = dp->partial;
     dp->partial_lse    = dp->partial ? dp->partial + rows * head_dim : nullptr;
+    dp->built_on_device = false;
     dp->num_ctas       = plan->num_ctas;
     dp->num_segments   = static_cast<int>(nseg);
     dp->num_items      = plan->num_items;
@@ -704,6 +713,114 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         if (dp->fused.valid) g_fused_registry[dp->segments] = dp->fused;
         else g_fused_registry.erase(dp->segments);
     }
+    return PD_OK;
+}
+
+// The plan of a step cut by plan_kernel from lengths that live on the device.  Nothing here waits for
+// the device or copies from the host; buffers only grow, so after a first call with the largest batch
+// later calls allocate nothing and the call can be captured into a CUDA graph together with the decode.
+int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, const int* d_slot_ids, int batch,
+                         int num_q_heads, int num_kv_heads, int head_dim, int num_ctas, void* stream_) {
+    if (!dp || (batch > 0 && !d_seq_lens)) return set_error(PD_INVALID_ARGUMENT, "device_plan_build: null argument");
+    if (batch < 0) return set_error(PD_INVALID_ARGUMENT, "device_plan_build: negative batch");
+    if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    const int group = num_q_heads / num_kv_heads;
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
+    int grid = num_ctas;
+    if (grid <= 0)
+        if (int rc = pd_default_ctas(dtype, head_dim, group, &grid)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    auto round16 = [](size_t x) { return (x + 15) & ~static_cast<size_t>(15); };
+    const size_t items = static_cast<size_t>(batch) * num_kv_heads;
+    const size_t cap_seg = items + grid;                       // every cut adds one segment: at most grid - 1 cuts
+    const size_t seg_bytes  = round16(sizeof(int4) * cap_seg);
+    const size_t cta_bytes  = round16(sizeof(int) * (grid + 1));
+    const size_t item_bytes = round16(sizeof(int) * (items + 1));
+    const size_t row_bytes  = round16(sizeof(int) * (batch + 1));
+    const size_t info_bytes = round16(sizeof(int) * pdk::PLAN_INFO_INTS);
+    const size_t total = seg_bytes + cta_bytes + item_bytes + row_bytes + info_bytes;
+    const void* old_key = dp->segments;
+    if (total > dp->arena_cap) {
+        PD_CUDA(cudaFree(dp->arena));
+        dp->arena = nullptr; dp->arena_cap = 0;
+        PD_CUDA(cudaMalloc(&dp->arena, total));
+        dp->arena_cap = total;
+    }
+    const size_t rows = cap_seg * group;
+    const size_t need = rows * (head_dim + 1) + items;
+    if (need > dp->partial_cap) {
+        PD_CUDA(cudaFree(dp->partial));
+        dp->partial = nullptr; dp->partial_cap = 0;
+        PD_CUDA(cudaMalloc(&dp->partial, sizeof(float) * need));
+        dp->partial_cap = need;
+    }
+    char* a = static_cast<char*>(dp->arena);
+    dp->segments        = a;
+    dp->cta_seg_begin   = reinterpret_cast<const int*>(a + seg_bytes);
+    dp->item_seg_begin  = reinterpret_cast<const int*>(a + seg_bytes + cta_bytes);
+    dp->row_tile_begin  = reinterpret_cast<int*>(a + seg_bytes + cta_bytes + item_bytes);
+    dp->info            = reinterpret_cast<int*>(a + seg_bytes + cta_bytes + item_bytes + row_bytes);
+    dp->partial_out     = dp->partial;
+    dp->partial_lse     = dp->partial + rows * head_dim;
+    dp->num_ctas        = grid;                  // the launch grid; CTAs past the cut's own count idle
+    dp->num_segments    = static_cast<int>(cap_seg);
+    dp->num_items       = static_cast<int>(items);
+    dp->needs_merge     = pdk::MERGE_HYBRID;     // how rows were cut is only known on the device
+    dp->built_on_device = true;
+    dp->tile            = k->tile;
+    dp->fused           = pd_device_plan::Fused{};
+    {
+        std::lock_guard<std::mutex> lock(g_fused_mutex);
+        if (old_key) g_fused_registry.erase(old_key);
+        g_fused_registry.erase(dp->segments);
+    }
+    pdk::PlanJob job{};
+    job.seq_lens = d_seq_lens; job.slot_ids = d_slot_ids;
+    job.batch = batch; job.num_kv_heads = num_kv_heads; job.group = group; job.tile = k->tile; job.grid = grid;
+    job.segments = reinterpret_cast<int4*>(a);
+    job.cta_seg_begin = const_cast<int*>(dp->cta_seg_begin);
+    job.item_seg_begin = const_cast<int*>(dp->item_seg_begin);
+    job.row_tile_begin = dp->row_tile_begin;
+    job.info = dp->info;
+    job.partial_lse = dp->partial_lse;
+    pdk::plan_kernel<<<1, pdk::PLAN_THREADS, 0, stream>>>(job);
+    PD_CUDA(cudaGetLastError());
+    return PD_OK;
+}
+
+int pd_device_plan_info(const pd_device_plan* dp, int* out, void* stream_) {
+    if (!dp || !out) return set_error(PD_INVALID_ARGUMENT, "device_plan_info: null argument");
+    if (!dp->built_on_device) return set_error(PD_INVALID_ARGUMENT, "device_plan_info: the plan was not built on the device");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PD_CUDA(cudaMemcpyAsync(out, dp->info, sizeof(int) * pdk::PLAN_INFO_INTS, cudaMemcpyDeviceToHost, stream));
+    PD_CUDA(cudaStreamSynchronize(stream));
+    return PD_OK;
+}
+
+int pd_device_plan_fetch(const pd_device_plan* dp, pd_plan** out, void* stream_) {
+    if (!dp || !out) return set_error(PD_INVALID_ARGUMENT, "device_plan_fetch: null argument");
+    int info[pdk::PLAN_INFO_INTS];
+    if (int rc = pd_device_plan_info(dp, info, stream_)) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    pd_plan* plan = new pd_plan();
+    plan->num_ctas = info[pdk::PLAN_INFO_CTAS];
+    plan->tile = dp->tile;
+    plan->num_items = dp->num_items;
+    plan->segments.resize(4 * static_cast<size_t>(info[pdk::PLAN_INFO_SEGMENTS]));
+    plan->cta_seg_begin.resize(plan->num_ctas + 1);
+    plan->item_seg_begin.resize(plan->num_items + 1);
+    cudaError_t e = cudaSuccess;
+    if (!plan->segments.empty())
+        e = cudaMemcpyAsync(plan->segments.data(), dp->segments, sizeof(int) * plan->segments.size(), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(plan->cta_seg_begin.data(), dp->cta_seg_begin, sizeof(int) * plan->cta_seg_begin.size(), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(plan->item_seg_begin.data(), dp->item_seg_begin, sizeof(int) * plan->item_seg_begin.size(), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) { delete plan; return set_error(PD_CUDA_ERROR, "device_plan_fetch: %s", cudaGetErrorString(e)); }
+    *out = plan;
     return PD_OK;
 }
 
@@ -1388,18 +1505,36 @@ int pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads,
     c->plan_batch = num_slots;
     c->plan_num_q_heads = num_q_heads;
     c->plan_identity = true;
+    c->plan_on_device = false;
     for (int i = 0; i < num_slots; i++) c->plan_identity = c->plan_identity && slots[i] == i;
+    return PD_OK;
+}
+
+int pd_cache_plan_device(pd_cache* c, const int* d_slot_ids, int batch, int num_q_heads, int num_ctas, void* stream) {
+    if (!c) return set_error(PD_INVALID_ARGUMENT, "plan_device: null cache");
+    if (batch < 0 || (!d_slot_ids && batch > c->cfg.max_slots))
+        return set_error(PD_INVALID_ARGUMENT, "plan_device: batch exceeds the cache's slots");
+    if (int rc = pd_device_plan_build(c->device_plan, c->cfg.dtype, c->d_seq_lens, d_slot_ids, batch, num_q_heads,
+                                      c->cfg.num_kv_heads, c->cfg.head_dim, num_ctas, stream))
+        return rc;
+    pd_plan_free(c->plan);
+    c->plan = nullptr;
+    c->plan_batch = batch;
+    c->plan_num_q_heads = num_q_heads;
+    c->plan_identity = d_slot_ids == nullptr;
+    c->plan_on_device = true;
+    c->plan_slot_ids = d_slot_ids;
     return PD_OK;
 }
 
 int pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream) {
     if (!c) return set_error(PD_INVALID_ARGUMENT, "run: null cache");
-    if (!c->plan) return set_error(PD_INVALID_ARGUMENT, "run: no plan; call plan() first");
+    if (!c->plan && !c->plan_on_device) return set_error(PD_INVALID_ARGUMENT, "run: no plan; call plan() first");
     pd_params p;
     pd_cache_params(c, &p);
     p.q = d_q;
     p.out = d_out;
-    p.slot_ids = c->plan_identity ? nullptr : c->d_slot_ids;   // row i reads slot i: skip the indirection
+    p.slot_ids = c->plan_identity ? nullptr : c->plan_on_device ? c->plan_slot_ids : c->d_slot_ids;   // row i reads slot i: skip the indirection
     p.batch = c->plan_batch;
     p.num_q_heads = c->plan_num_q_heads;
     pd_device_plan_bind(c->device_plan, &p);

@@ -160,6 +160,27 @@ class DevicePlan:
     def bind(self, params):
         check(_lib.lib().pd_device_plan_bind(self._h, C.byref(params)))
 
+    def build(self, dtype, d_seq_lens, batch, num_q_heads, num_kv_heads, head_dim=128, num_ctas=0, d_slot_ids=None,
+              stream=0):
+        """Cut the step's plan on the device from device-resident lengths (no counterpart in the
+        reference): same arrays as make_plan + upload, no host copy, no wait, capturable in a CUDA graph
+        once the buffers have grown to the largest batch."""
+        check(_lib.lib().pd_device_plan_build(self._h, int(dtype), _ptr(d_seq_lens), _ptr(d_slot_ids), batch, num_q_heads,
+                                              num_kv_heads, head_dim, num_ctas, stream))
+
+    def info(self, stream=0):
+        """(CTAs with work, segments, most pieces of any (row, kv head), 1 + first row with a bad length) of a
+        plan built on the device; waits for the stream."""
+        out = (C.c_int * 4)()
+        check(_lib.lib().pd_device_plan_info(self._h, out, stream))
+        return tuple(out)
+
+    def fetch(self, stream=0):
+        """The device-built plan as a host DecodePlan; waits for the stream."""
+        h = C.c_void_p()
+        check(_lib.lib().pd_device_plan_fetch(self._h, C.byref(h), stream))
+        return DecodePlan(h)
+
 
 def paged_decode(dtype, params, stream=0, num_pages=0):
     """decode::paged_decode (src/decode/decode.hpp:66)."""
@@ -269,6 +290,11 @@ class PagedKVCache:
     def plan(self, slots, num_q_heads, num_ctas=0, stream=0):
         s = np.ascontiguousarray(slots, dtype=np.int32)
         check(_lib.lib().pd_cache_plan(self._h, s.ctypes.data_as(C.POINTER(C.c_int)), len(s), num_q_heads, num_ctas, stream))
+
+    def plan_device(self, batch, num_q_heads, num_ctas=0, d_slot_ids=None, stream=0):
+        """plan() cut on the device from the cache's device-side lengths (slots 0..batch-1, or the device
+        array d_slot_ids); nothing is copied from the host and the call does not wait."""
+        check(_lib.lib().pd_cache_plan_device(self._h, _ptr(d_slot_ids), batch, num_q_heads, num_ctas, stream))
 
     def run(self, d_q, d_out, stream=0):
         check(_lib.lib().pd_cache_run(self._h, _ptr(d_q), _ptr(d_out), stream))

@@ -95,6 +95,15 @@ public:
     }
     void bind(DecodeParams& p) const { check(pd_device_plan_bind(h_, as_pd(p))); }
 
+    // Not in the reference: the same plan cut on the device from device-resident lengths (row b has
+    // d_seq_lens[d_slot_ids ? d_slot_ids[b] : b]).  No host copy, no wait; allocation-free once the buffers
+    // have grown to the largest batch, so it can be captured into a CUDA graph with the decode after it.
+    void build(KVDtype dtype, const int* d_seq_lens, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+               int num_ctas = 0, const int* d_slot_ids = nullptr, cudaStream_t stream = 0) {
+        check(pd_device_plan_build(h_, static_cast<int>(dtype), d_seq_lens, d_slot_ids, batch, num_q_heads, num_kv_heads,
+                                   head_dim, num_ctas, stream));
+    }
+
 private:
     pd_device_plan* h_ = nullptr;
 };

@@ -52,6 +52,12 @@ public:
         check(pd_cache_plan(h_, slots.data(), static_cast<int>(slots.size()), num_q_heads, num_ctas, stream));
         plan_ = detail::to_plan(pd_cache_last_plan(h_));
     }
+    // Not in the reference: plan() cut on the device from the cache's device-side lengths (slots
+    // 0..batch-1, or the device array d_slot_ids).  last_plan() is empty afterwards.
+    void plan_device(int batch, int num_q_heads, int num_ctas = 0, const int* d_slot_ids = nullptr, cudaStream_t stream = 0) {
+        check(pd_cache_plan_device(h_, d_slot_ids, batch, num_q_heads, num_ctas, stream));
+        plan_ = DecodePlan{};
+    }
     void run(const half* d_q, half* d_out, cudaStream_t stream = 0) { check(pd_cache_run(h_, d_q, d_out, stream)); }
     void decode(const half* d_q, half* d_out, int batch, int num_q_heads, int num_ctas = 0, cudaStream_t stream = 0) {
         check(pd_cache_decode(h_, d_q, d_out, batch, num_q_heads, num_ctas, stream));
