@@ -182,6 +182,12 @@ int  pd_device_plan_fetch(const pd_device_plan* dp, pd_plan** out, void* stream)
  * pd_paged_decode passes "unknown". */
 int pd_paged_decode(int dtype, const pd_params* p, void* stream);
 int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* stream);
+/* No counterpart in the reference, which has one dequantisation scale per tensor (DecodeParams::k_scale,
+ * v_scale; its README notes that per-head scales would help fp8 accuracy).  The same decode with one
+ * scale per kv head: d_k_scales / d_v_scales are device arrays of num_kv_heads floats that replace
+ * p->k_scale / p->v_scale (either may be NULL: the per-tensor value then applies). */
+int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const float* d_k_scales,
+                           const float* d_v_scales, void* stream);
 
 /* No counterpart in the reference (its DevicePlan always allocates, src/decode/decode.cu:131-141).
  * The same decode + merge as pd_paged_decode_bounded, for callers that cannot allow a device
@@ -261,6 +267,13 @@ int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream);
 int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
                      const int* d_block_table_row, int start_pos, int n, int num_kv_heads,
                      int head_dim, int page_size, float k_scale, float v_scale, void* stream);
+/* The same with one quantisation scale per kv head (device arrays of num_kv_heads floats; NULL: the
+ * per-tensor scale): byte = e4m3(value * (1 / scale[head])), reciprocal correctly rounded.  No
+ * counterpart in the reference. */
+int pd_append_tokens_scaled(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
+                            const int* d_block_table_row, int start_pos, int n, int num_kv_heads,
+                            int head_dim, int page_size, float k_scale, float v_scale,
+                            const float* d_k_scales, const float* d_v_scales, void* stream);
 
 /* decode::PagedKVCache (src/decode/paged_kv_cache.hpp:31-73). */
 size_t pd_cache_bytes_per_page(const pd_cache_config* cfg);
@@ -279,6 +292,10 @@ int    pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, 
 int    pd_cache_append_batch(pd_cache* c, int count, const int* slots, const void* const* d_k,
                              const void* const* d_v, const int* n, void* stream);
 int    pd_cache_release(pd_cache* c, int slot);
+/* Per-kv-head scales for an fp8 cache (host arrays of num_kv_heads positive floats; both NULL: back to
+ * the per-tensor scales of the config).  Every later append quantises and every later run dequantises
+ * with them.  Only while the cache holds no tokens.  No counterpart in the reference. */
+int    pd_cache_set_head_scales(pd_cache* c, const float* k_scales, const float* v_scales);
 void   pd_cache_shuffle_free_pages(pd_cache* c, unsigned seed);
 int    pd_cache_plan(pd_cache* c, const int* slots, int num_slots, int num_q_heads, int num_ctas, void* stream);
 /* plan() through the device-side planner (pd_device_plan_build) from the cache's own device lengths, which

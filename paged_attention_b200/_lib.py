@@ -101,6 +101,10 @@ SIGNATURES = {
     "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
     "pd_append_tokens": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_float, C.c_float, _vp]),
+    "pd_append_tokens_scaled": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.c_float, C.c_float, _vp, _vp, _vp]),
+    "pd_paged_decode_scaled": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp, _vp, _vp]),
+    "pd_cache_set_head_scales": (C.c_int, [_vp, _vp, _vp]),
     "pd_cache_bytes_per_page": (C.c_size_t, [C.POINTER(pd_cache_config)]),
     "pd_cache_pages_for_budget": (C.c_int, [C.POINTER(pd_cache_config), C.c_size_t]),
     "pd_cache_create": (C.c_int, [C.POINTER(pd_cache_config), C.POINTER(_vp)]),

@@ -31,9 +31,18 @@ struct AppendJob {
     int           first_unit; // prefix sum of units over jobs (batched launch)
 };
 
+// Optional per-kv-head quantisation scales (device arrays of num_kv_heads floats, or null: the per-tensor
+// factors apply).  The stored byte is e4m3(x * (1 / scale[h])) with the reciprocal correctly rounded, the
+// same arithmetic as the per-tensor path.  The reference has one scale per tensor only.
+struct AppendHeadScales {
+    const float* k;
+    const float* v;
+};
+
 template<bool FP8>
 __device__ __forceinline__ void append_unit(const AppendJob& job, int unit, void* k_cache, void* v_cache,
-                                            int num_kv_heads, int page_size, float inv_k, float inv_v)
+                                            int num_kv_heads, int page_size, float inv_k, float inv_v,
+                                            const AppendHeadScales& hs = AppendHeadScales{nullptr, nullptr})
 {
     constexpr int D = 128, VEC = 8, PER_ROW = D / VEC;   // 16 threads per (token, head) row
     const int c = unit % PER_ROW;
@@ -46,6 +55,8 @@ __device__ __forceinline__ void append_unit(const AppendJob& job, int unit, void
     const uint4 kx = *reinterpret_cast<const uint4*>(job.k + src);
     const uint4 vx = *reinterpret_cast<const uint4*>(job.v + src);
     if constexpr (FP8) {
+        if (hs.k) inv_k = __frcp_rn(__ldg(hs.k + h));
+        if (hs.v) inv_v = __frcp_rn(__ldg(hs.v + h));
         uint2 kq, vq;
         kq.x = quant4_e4m3(kx.x, kx.y, inv_k); kq.y = quant4_e4m3(kx.z, kx.w, inv_k);
         vq.x = quant4_e4m3(vx.x, vx.y, inv_v); vq.y = quant4_e4m3(vx.z, vx.w, inv_v);
@@ -60,11 +71,11 @@ __device__ __forceinline__ void append_unit(const AppendJob& job, int unit, void
 template<bool FP8>
 __global__ void __launch_bounds__(256)
 append_kernel(AppendJob job, void* k_cache, void* v_cache, int num_kv_heads, int page_size,
-              float inv_k, float inv_v)
+              float inv_k, float inv_v, AppendHeadScales hs)
 {
     const int units = job.n * num_kv_heads * 16;
     for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < units; u += gridDim.x * blockDim.x)
-        append_unit<FP8>(job, u, k_cache, v_cache, num_kv_heads, page_size, inv_k, inv_v);
+        append_unit<FP8>(job, u, k_cache, v_cache, num_kv_heads, page_size, inv_k, inv_v, hs);
 }
 
 // Many slots in one launch: jobs[] lives in device memory, first_unit is the
@@ -72,7 +83,7 @@ append_kernel(AppendJob job, void* k_cache, void* v_cache, int num_kv_heads, int
 template<bool FP8>
 __global__ void __launch_bounds__(256)
 append_batch_kernel(const AppendJob* __restrict__ jobs, int num_jobs, int total_units, void* k_cache,
-                    void* v_cache, int num_kv_heads, int page_size, float inv_k, float inv_v)
+                    void* v_cache, int num_kv_heads, int page_size, float inv_k, float inv_v, AppendHeadScales hs)
 {
     for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < total_units; u += gridDim.x * blockDim.x) {
         int lo = 0, hi = num_jobs - 1;
@@ -81,7 +92,7 @@ append_batch_kernel(const AppendJob* __restrict__ jobs, int num_jobs, int total_
             if (jobs[mid].first_unit <= u) lo = mid; else hi = mid - 1;
         }
         const AppendJob job = jobs[lo];
-        append_unit<FP8>(job, u - job.first_unit, k_cache, v_cache, num_kv_heads, page_size, inv_k, inv_v);
+        append_unit<FP8>(job, u - job.first_unit, k_cache, v_cache, num_kv_heads, page_size, inv_k, inv_v, hs);
     }
 }
 

@@ -65,6 +65,13 @@ constexpr unsigned ST_GATHER_TIMEOUT = 5;  // a peer's "slice has landed" flag n
 // is stored straight into the gathered buffer of every peer (plain peer stores over NVLink; the
 // local buffer is out[rank]).  When the last CTA of the grid is done, flags[r][rank] = epoch tells
 // peer r that this rank's slice has landed.  No collective call follows the kernel.
+// Optional per-kv-head dequantisation scales (device arrays of num_kv_heads floats, or null: the
+// per-tensor pd_params::k_scale / v_scale apply).  The reference has one scale per tensor only.
+struct HeadScales {
+    const float* k;
+    const float* v;
+};
+
 constexpr int MAX_GATHER = 8;
 struct GatherOut {
     int       world;
@@ -526,7 +533,8 @@ template<typename KV, int GROUP, typename C>
 __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const int btl_flags /* log2(box tokens) | diagnostic flags */,
-                    unsigned* __restrict__ status, const __grid_constant__ GatherOut gp)
+                    unsigned* __restrict__ status, const __grid_constant__ GatherOut gp,
+                    const __grid_constant__ HeadScales hs)
 {
     const int  btl     = btl_flags & 0xff;
     const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
@@ -690,7 +698,13 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     // ================= consumer warps =================
     const int g  = lane >> 2;   // fragment row
     const int qd = lane & 3;    // fragment column pair: this lane owns heads 2qd, 2qd+1
-    const float qk_scale = p.sm_scale * p.k_scale * 1.4426950408889634f;   // softmax runs in base 2
+    // softmax runs in base 2; with per-head scales the factor belongs to the segment's kv head
+    float qk_scale = p.sm_scale * p.k_scale * 1.4426950408889634f;
+    float v_scale  = p.v_scale;
+    if constexpr (S::HEADS > 1) {
+        if (hs.k) qk_scale = p.sm_scale * __ldg(hs.k + warp) * 1.4426950408889634f;
+        if (hs.v) v_scale = __ldg(hs.v + warp);
+    }
 
     float acc[8][4];
     float m_run[2], l_run[2];
@@ -714,6 +728,10 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     for (int seg = seg_begin; alive && seg < seg_end; seg++) {
         const int4 sg = __ldg(segments + seg);
         bool need_q = true;   // Q^T fragments are read from the slot of the segment's first tile
+        if constexpr (S::HEADS == 1) {
+            if (hs.k) qk_scale = p.sm_scale * __ldg(hs.k + sg.y) * 1.4426950408889634f;
+            if (hs.v) v_scale = __ldg(hs.v + sg.y);
+        }
         if constexpr (S::HEADS > 1) {
             // head-fused: this warp's kv head is `warp`; its query rows come straight from global memory
             const bool live = g < GROUP;
@@ -808,7 +826,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                     const int hd = 2 * qd + h;
                     if (hd < GROUP) {
                         const int hq = warp * GROUP + hd;
-                        const float inv = p.v_scale / l[h];
+                        const float inv = v_scale / l[h];
                         const size_t prow = (static_cast<size_t>(seg) * p.num_q_heads + hq) * HEAD_DIM;
                         const size_t orow = out_index(p, gp, sg.x, hq);
 #pragma unroll
@@ -882,7 +900,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                         num = fmaf(wt, w_o[(w * S::GROUP_PAD + hl) * OSTRIDE + d], num);
                         den = fmaf(wt, w_l[w * 8 + hd], den);
                     }
-                    const float o = num / den * p.v_scale;
+                    const float o = num / den * v_scale;
                     if (whole) {
                         store_out(p, gp, out_index(p, gp, sg.x, sg.y * GROUP + hd) + d, __float2half(o));
                     } else {

@@ -78,15 +78,16 @@ constexpr int NUM_VARIANTS = 5;
 struct KernelInfo {
     const void* fn;
     int tile, threads, smem, per_sm;
-    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&, cudaStream_t);
+    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&,
+                   const pdk::HeadScales&, cudaStream_t);
     void (*merge)(const pd_params&, cudaStream_t);
 };
 
 template<typename KV, int GROUP, typename C>
 void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl,
-                   unsigned* status, const pdk::GatherOut& gather, cudaStream_t stream) {
+                   unsigned* status, const pdk::GatherOut& gather, const pdk::HeadScales& scales, cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
-    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather);
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales);
 }
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
@@ -436,6 +437,7 @@ struct pd_cache {
     pd_device_plan* device_plan = nullptr;
     int plan_batch = 0, plan_num_q_heads = 0;
     bool plan_identity = false;
+    float* d_head_scales = nullptr;       // optional per-kv-head scales: k[num_kv_heads] then v[num_kv_heads]
     bool plan_on_device = false;          // the current plan was cut by pd_cache_plan_device
     const int* plan_slot_ids = nullptr;   // ... for these rows (device pointer of the caller, or null)
     std::vector<int> free_pages;
@@ -841,7 +843,8 @@ int pd_device_plan_bind(const pd_device_plan* dp, pd_params* p) {
 }  // extern "C"
 
 namespace {
-int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherOut& gather, void* stream_) {
+int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherOut& gather, void* stream_,
+                const pdk::HeadScales& scales = pdk::HeadScales{nullptr, nullptr}) {
     if (!p) return set_error(PD_INVALID_ARGUMENT, "paged_decode: null params");
     if (p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
         return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
@@ -912,7 +915,7 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     static const int stage_limit = std::getenv("PD_B200_STAGE_LIMIT") ? (std::atoi(std::getenv("PD_B200_STAGE_LIMIT")) & 0xf) : 0;
     k->launch(*p, k_map, v_map,
               btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
-              status, gather, stream);
+              status, gather, scales, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, stream);
@@ -930,6 +933,11 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
 
 int pd_paged_decode(int dtype, const pd_params* p, void* stream) {
     return pd_paged_decode_bounded(dtype, p, 0, stream);
+}
+
+int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const float* d_k_scales, const float* d_v_scales,
+                           void* stream) {
+    return decode_impl(dtype, p, num_pages, pdk::GatherOut{}, stream, pdk::HeadScales{d_k_scales, d_v_scales});
 }
 
 // ---- decode without any allocation -------------------------------------------------------------------------
@@ -1024,7 +1032,7 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, stream);
+    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, pdk::HeadScales{nullptr, nullptr}, stream);
     PD_CUDA(cudaGetLastError());
     if (local.needs_merge) {
         k->merge(local, stream);
@@ -1072,9 +1080,10 @@ int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream_) {
 
 // ---- append ------------------------------------------------------------------------------------------------
 
-int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
-                     const int* d_block_table_row, int start_pos, int n, int num_kv_heads, int head_dim,
-                     int page_size, float k_scale, float v_scale, void* stream_) {
+int pd_append_tokens_scaled(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
+                            const int* d_block_table_row, int start_pos, int n, int num_kv_heads, int head_dim,
+                            int page_size, float k_scale, float v_scale, const float* d_k_scales, const float* d_v_scales,
+                            void* stream_) {
     if (dtype != PD_FP16 && dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "unsupported KV dtype %d", dtype);
     if (head_dim != 128) return set_error(PD_INVALID_ARGUMENT, "append: head_dim must be 128");
     if (n <= 0) return PD_OK;
@@ -1088,12 +1097,21 @@ int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache,
     const long long units = static_cast<long long>(n) * num_kv_heads * 16;
     const int blocks = static_cast<int>(std::min<long long>((units + 255) / 256, 148 * 16));
     if (dtype == PD_FP16)
-        pdk::append_kernel<false><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size, 1.f, 1.f);
+        pdk::append_kernel<false><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size, 1.f, 1.f,
+                                                              pdk::AppendHeadScales{nullptr, nullptr});
     else
         pdk::append_kernel<true><<<blocks, 256, 0, stream>>>(job, k_cache, v_cache, num_kv_heads, page_size,
-                                                             1.f / k_scale, 1.f / v_scale);
+                                                             1.f / k_scale, 1.f / v_scale,
+                                                             pdk::AppendHeadScales{d_k_scales, d_v_scales});
     PD_CUDA(cudaGetLastError());
     return PD_OK;
+}
+
+int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache, void* v_cache,
+                     const int* d_block_table_row, int start_pos, int n, int num_kv_heads, int head_dim,
+                     int page_size, float k_scale, float v_scale, void* stream) {
+    return pd_append_tokens_scaled(dtype, d_k, d_v, k_cache, v_cache, d_block_table_row, start_pos, n, num_kv_heads,
+                                   head_dim, page_size, k_scale, v_scale, nullptr, nullptr, stream);
 }
 
 // ---- outputs gathered over the GPUs of a node by peer stores ---------------------------------------------------
@@ -1250,6 +1268,7 @@ void pd_cache_destroy(pd_cache* c) {
     cudaFree(c->d_block_table);
     cudaFree(c->d_seq_lens);
     cudaFree(c->d_slot_ids);
+    cudaFree(c->d_head_scales);
     if (c->batch_staged) { cudaEventSynchronize(c->batch_staged); cudaEventDestroy(c->batch_staged); }
     cudaFreeHost(c->batch_staging);
     cudaFree(c->batch_device);
@@ -1333,8 +1352,9 @@ int pd_cache_append(pd_cache* c, int slot, const void* d_k, const void* d_v, int
                                 cudaMemcpyHostToDevice, stream));
     c->seq_lens[slot] = new_len;
     PD_CUDA(cudaMemcpyAsync(c->d_seq_lens + slot, &c->seq_lens[slot], sizeof(int), cudaMemcpyHostToDevice, stream));
-    if (int rc = pd_append_tokens(c->cfg.dtype, d_k, d_v, c->d_k, c->d_v, row, old_len, n, c->cfg.num_kv_heads,
-                                  c->cfg.head_dim, ps, c->cfg.k_scale, c->cfg.v_scale, stream))
+    if (int rc = pd_append_tokens_scaled(c->cfg.dtype, d_k, d_v, c->d_k, c->d_v, row, old_len, n, c->cfg.num_kv_heads,
+                                         c->cfg.head_dim, ps, c->cfg.k_scale, c->cfg.v_scale, c->d_head_scales,
+                                         c->d_head_scales ? c->d_head_scales + c->cfg.num_kv_heads : nullptr, stream))
         return rc;
     // As in the reference (src/decode/paged_kv_cache.cu:133-134) the call returns with the tokens in place.
     PD_CUDA(cudaStreamSynchronize(stream));
@@ -1431,12 +1451,13 @@ int pd_cache_append_batch(pd_cache* c, int count, const int* slots, const void* 
         const int blocks = static_cast<int>(std::min<long long>((units + 255) / 256, 148 * 16));
         const bool fp8 = c->cfg.dtype == PD_FP8_E4M3;
         const float ik = fp8 ? 1.f / c->cfg.k_scale : 1.f, iv = fp8 ? 1.f / c->cfg.v_scale : 1.f;
+        const pdk::AppendHeadScales hs{c->d_head_scales, c->d_head_scales ? c->d_head_scales + c->cfg.num_kv_heads : nullptr};
         if (fp8)
             pdk::append_batch_kernel<true><<<blocks, 256, 0, stream>>>(reinterpret_cast<const pdk::AppendJob*>(d), live,
-                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv);
+                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv, hs);
         else
             pdk::append_batch_kernel<false><<<blocks, 256, 0, stream>>>(reinterpret_cast<const pdk::AppendJob*>(d), live,
-                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv);
+                static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv, hs);
         PD_CUDA(cudaGetLastError());
     }
     return PD_OK;
@@ -1538,7 +1559,29 @@ int pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream) {
     p.batch = c->plan_batch;
     p.num_q_heads = c->plan_num_q_heads;
     pd_device_plan_bind(c->device_plan, &p);
-    return pd_paged_decode_bounded(c->cfg.dtype, &p, c->cfg.num_pages, stream);
+    return pd_paged_decode_scaled(c->cfg.dtype, &p, c->cfg.num_pages, c->d_head_scales,
+                                  c->d_head_scales ? c->d_head_scales + c->cfg.num_kv_heads : nullptr, stream);
+}
+
+int pd_cache_set_head_scales(pd_cache* c, const float* k_scales, const float* v_scales) {
+    if (!c) return set_error(PD_INVALID_ARGUMENT, "set_head_scales: null cache");
+    if (c->cfg.dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "set_head_scales: only an fp8 cache is quantised");
+    if ((k_scales == nullptr) != (v_scales == nullptr))
+        return set_error(PD_INVALID_ARGUMENT, "set_head_scales: give both arrays or neither");
+    for (int len : c->seq_lens)
+        if (len > 0) return set_error(PD_INVALID_ARGUMENT, "set_head_scales: the cache already holds tokens quantised with the old scales");
+    if (!k_scales) {
+        PD_CUDA(cudaFree(c->d_head_scales));
+        c->d_head_scales = nullptr;
+        return PD_OK;
+    }
+    const int n = c->cfg.num_kv_heads;
+    for (int h = 0; h < n; h++)
+        if (!(k_scales[h] > 0.f) || !(v_scales[h] > 0.f)) return set_error(PD_INVALID_ARGUMENT, "set_head_scales: scales must be positive");
+    if (!c->d_head_scales) PD_CUDA(cudaMalloc(&c->d_head_scales, sizeof(float) * 2 * n));
+    PD_CUDA(cudaMemcpy(c->d_head_scales, k_scales, sizeof(float) * n, cudaMemcpyHostToDevice));
+    PD_CUDA(cudaMemcpy(c->d_head_scales + n, v_scales, sizeof(float) * n, cudaMemcpyHostToDevice));
+    return PD_OK;
 }
 
 int pd_cache_decode(pd_cache* c, const void* d_q, void* d_out, int batch, int num_q_heads, int num_ctas, void* stream) {

@@ -182,9 +182,14 @@ class DevicePlan:
         return DecodePlan(h)
 
 
-def paged_decode(dtype, params, stream=0, num_pages=0):
-    """decode::paged_decode (src/decode/decode.hpp:66)."""
-    check(_lib.lib().pd_paged_decode_bounded(int(dtype), C.byref(params), num_pages, stream))
+def paged_decode(dtype, params, stream=0, num_pages=0, d_k_scales=None, d_v_scales=None):
+    """decode::paged_decode (src/decode/decode.hpp:66).  d_k_scales / d_v_scales (not in the reference):
+    device arrays of one dequantisation scale per kv head, replacing params.k_scale / v_scale."""
+    if d_k_scales is None and d_v_scales is None:
+        check(_lib.lib().pd_paged_decode_bounded(int(dtype), C.byref(params), num_pages, stream))
+    else:
+        check(_lib.lib().pd_paged_decode_scaled(int(dtype), C.byref(params), num_pages, _ptr(d_k_scales), _ptr(d_v_scales),
+                                                stream))
 
 
 def paged_decode_static(dtype, params, num_segments, stream=0, num_pages=0, d_status=None):
@@ -208,11 +213,12 @@ def stream_read(d_buf, nbytes, blocks, stream=0):
 
 
 def append_tokens(dtype, d_k, d_v, k_cache, v_cache, d_block_table_row, start_pos, n, num_kv_heads, head_dim,
-                  page_size, k_scale=1.0, v_scale=1.0, stream=0):
-    """append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers."""
-    check(_lib.lib().pd_append_tokens(int(dtype), _ptr(d_k), _ptr(d_v), _ptr(k_cache), _ptr(v_cache),
-                                      _ptr(d_block_table_row), start_pos, n, num_kv_heads, head_dim, page_size,
-                                      k_scale, v_scale, stream))
+                  page_size, k_scale=1.0, v_scale=1.0, stream=0, d_k_scales=None, d_v_scales=None):
+    """append_kernel<KV> (src/decode/paged_kv_cache.cu:25-39) on caller-owned buffers.  d_k_scales /
+    d_v_scales (not in the reference): device arrays of one quantisation scale per kv head."""
+    check(_lib.lib().pd_append_tokens_scaled(int(dtype), _ptr(d_k), _ptr(d_v), _ptr(k_cache), _ptr(v_cache),
+                                             _ptr(d_block_table_row), start_pos, n, num_kv_heads, head_dim, page_size,
+                                             k_scale, v_scale, _ptr(d_k_scales), _ptr(d_v_scales), stream))
 
 
 class PagedKVCache:
@@ -286,6 +292,17 @@ class PagedKVCache:
 
     def shuffle_free_pages(self, seed):
         _lib.lib().pd_cache_shuffle_free_pages(self._h, seed)
+
+    def set_head_scales(self, k_scales, v_scales):
+        """One fp8 scale per kv head instead of one per tensor (not in the reference); None, None restores
+        the per-tensor scales.  Only while the cache is empty."""
+        arrays = []
+        for scales in (k_scales, v_scales):
+            a = None if scales is None else np.ascontiguousarray(scales, dtype=np.float32)
+            if a is not None and a.shape != (self._cfg.num_kv_heads,):
+                raise _lib.InvalidArgument("set_head_scales: one scale per kv head is needed")
+            arrays.append(a)
+        check(_lib.lib().pd_cache_set_head_scales(self._h, *[None if a is None else a.ctypes.data for a in arrays]))
 
     def plan(self, slots, num_q_heads, num_ctas=0, stream=0):
         s = np.ascontiguousarray(slots, dtype=np.int32)

@@ -46,6 +46,13 @@ public:
         return true;
     }
     void release(int slot) { check(pd_cache_release(h_, slot)); }
+    // Not in the reference: one fp8 scale per kv head (num_kv_heads positive floats each) instead of the
+    // per-tensor scales of the config; only while the cache holds no tokens.
+    void set_head_scales(const std::vector<float>& k_scales, const std::vector<float>& v_scales) {
+        if (k_scales.size() != v_scales.size()) throw std::invalid_argument("set_head_scales: sizes differ");
+        check(pd_cache_set_head_scales(h_, k_scales.empty() ? nullptr : k_scales.data(),
+                                       v_scales.empty() ? nullptr : v_scales.data()));
+    }
     void shuffle_free_pages(unsigned seed) { pd_cache_shuffle_free_pages(h_, seed); }
 
     void plan(const std::vector<int>& slots, int num_q_heads, int num_ctas = 0, cudaStream_t stream = 0) {
