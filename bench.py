@@ -301,7 +301,8 @@ def our_arm(args, wl):
             def __init__(self, ptr, n):
                 self.__cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
         gathered_views = [torch.as_tensor(_Dev(gg.buffer_ptr(i), full_bytes), device="cuda") for i in (0, 1)]
-        full_host = torch.empty(full_bytes, dtype=torch.uint8).pin_memory()
+        share = full_bytes // world      # each rank returns its 1/world of the gathered result to the host
+        full_host = torch.empty(share, dtype=torch.uint8).pin_memory()
 
     # Drive the kernel through the plan API, as a serving engine does: plan once per step, run per layer.
     plan = pa.make_plan(pa.KVDtype(dtype), lens, l_hq, l_hkv, 128, args.ctas)
@@ -338,8 +339,8 @@ def our_arm(args, wl):
     def step_e2e():
         q.copy_(q_host, non_blocking=True)
         step()
-        if gather_mode == "peer":     # the whole gathered result of this step comes back to the host
-            full_host.copy_(gathered_views[step_counter[0] & 1], non_blocking=True)
+        if gather_mode == "peer":     # the gathered result comes back to the host once, one share per rank
+            full_host.copy_(gathered_views[step_counter[0] & 1][rank * share:(rank + 1) * share], non_blocking=True)
         elif gather_mode == "nccl":
             out_host.copy_(gathered[rank * l_B:(rank + 1) * l_B], non_blocking=True)
         else:
@@ -435,7 +436,7 @@ def our_arm(args, wl):
                          "kernel_ms": per_decode, "frac_of_8TBps_nominal": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": per_e2e,
                     "h2d_bytes_per_step": q_host.numel() * 2,
-                    "d2h_bytes_per_step": full_bytes if gather_mode == "peer" else out_host.numel() * 2,
+                    "d2h_bytes_per_step": full_bytes // world if gather_mode == "peer" else out_host.numel() * 2,
                     "note": "pinned q -> device, decode+merge, out -> pinned host, per step; the KV cache is resident state"},
             "e2e_host_pointers": None if ms_direct is None else {
                 "value": job_bytes / (sum(ms_direct) / args.steps * 1e-3) / 1e9, "unit": "GB/s",
