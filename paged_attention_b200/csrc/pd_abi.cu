@@ -557,6 +557,35 @@ int pd_plan_from_arrays(int num_ctas, int tile, const int* segments, int num_seg
     plan->segments.assign(segments, segments + 4 * static_cast<size_t>(num_segments));
     plan->cta_seg_begin.assign(cta_seg_begin, cta_seg_begin + num_ctas + 1);
     plan->item_seg_begin.assign(item_seg_begin, item_seg_begin + num_items + 1);
+    // If the arrays describe a regular layer (items in (row, kv head) order, every item covering its
+    // row's tokens from 0 without gaps, the same length for all heads of a row), remember the layer so
+    // that the device plan can also carry the head-fused schedule; the KV dtype stays unknown (-2).
+    if (num_segments > 0) {
+        int rows = 0, heads = 0;
+        for (int s = 0; s < num_segments; s++) {
+            rows = std::max(rows, segments[4 * s] + 1);
+            heads = std::max(heads, segments[4 * s + 1] + 1);
+        }
+        bool regular = static_cast<long long>(rows) * heads == num_items;
+        std::vector<int> lens(regular ? rows : 0, 0);
+        for (int i = 0; regular && i < num_items; i++) {
+            const int b = i / heads, h = i % heads;
+            int at = 0;
+            for (int s = item_seg_begin[i]; regular && s < item_seg_begin[i + 1]; s++) {
+                const int* g = segments + 4 * s;
+                regular = g[0] == b && g[1] == h && g[2] == at;
+                at = g[3];
+            }
+            if (regular && h == 0) lens[b] = at;
+            regular = regular && at > 0 && at == lens[b];
+        }
+        if (regular) {
+            plan->dtype = -2;
+            plan->batch = rows;
+            plan->num_kv_heads = heads;
+            plan->seq_lens = std::move(lens);
+        }
+    }
     *out = plan;
     return PD_OK;
 }
@@ -602,8 +631,9 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // pd_make_plan) and the layer has exactly 8 kv heads: rows are the work items, 16 tokens the unit.
     pd_plan* rows_plan = nullptr;
     const KernelInfo* fk = nullptr;
-    if (plan->dtype == PD_FP16 && plan->num_kv_heads == FUSED_HEADS && plan->batch > 0 && plan->num_q_heads / plan->num_kv_heads == group &&
-        head_dim == 128) {
+    const bool layer_known = plan->dtype == PD_FP16 || plan->dtype == -2;   // -2: rebuilt from arrays, dtype checked at decode
+    if (layer_known && plan->num_kv_heads == FUSED_HEADS && plan->batch > 0 &&
+        (plan->num_q_heads == 0 || plan->num_q_heads / plan->num_kv_heads == group) && head_dim == 128) {
         fk = fused_info<__half>(group);
         int grid = plan->forced_ctas;
         if (fk && grid <= 0) {
@@ -660,7 +690,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // between launches: the merging warp re-arms its counter).
     const size_t rows = nseg * group;
     const size_t std_need = rows * (head_dim + 1) + plan->num_items;
-    const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * plan->num_q_heads : 0;
+    const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * static_cast<size_t>(group) * FUSED_HEADS : 0;
     const size_t f_need = rows_plan ? frows * (head_dim + 1) + plan->num_items : 0;
     const size_t need = std_need + f_need;
     if (need > dp->partial_cap) {
@@ -881,7 +911,8 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
         const KernelInfo* fk = dtype == PD_FP16 ? fused_info<__half>(p->num_q_heads / p->num_kv_heads) : nullptr;
         // Mode 1 keeps the (row, kv head) schedule where rows would be spread over more than 4 CTAs each.
         const bool wins = g_head_fused == 2 || f.needs_merge != pdk::MERGE_SEPARATE;
-        if (found && fk && wins && f.dtype == dtype && f.batch == p->batch && f.group == p->num_q_heads / p->num_kv_heads) {
+        if (found && fk && wins && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch &&
+            f.group == p->num_q_heads / p->num_kv_heads) {
             fused_params = *p;
             fused_params.segments = f.segments;
             fused_params.cta_seg_begin = f.cta_seg_begin;

@@ -133,6 +133,19 @@ def make_plan(dtype, seq_lens, num_q_heads, num_kv_heads, head_dim, num_ctas=0):
     return DecodePlan(h)
 
 
+def plan_from_arrays(num_ctas, tile, segments, cta_seg_begin, item_seg_begin):
+    """A DecodePlan from the arrays of a decode::DecodePlan made elsewhere (src/decode/decode.hpp:21-27),
+    e.g. by the reference's own planner; the tables are checked for consistency."""
+    seg = np.ascontiguousarray(segments, dtype=np.int32).reshape(-1, 4)
+    cta = np.ascontiguousarray(cta_seg_begin, dtype=np.int32)
+    item = np.ascontiguousarray(item_seg_begin, dtype=np.int32)
+    ip = C.POINTER(C.c_int)
+    h = C.c_void_p()
+    check(_lib.lib().pd_plan_from_arrays(num_ctas, tile, seg.ctypes.data_as(ip), len(seg), cta.ctypes.data_as(ip),
+                                         item.ctypes.data_as(ip), len(item) - 1, C.byref(h)))
+    return DecodePlan(h)
+
+
 def make_plan_tiled(tile, seq_lens, num_q_heads, num_kv_heads, num_ctas):
     """The planner with an explicit tile size; host arithmetic only."""
     lens, p = _lens_arg(seq_lens)
@@ -361,4 +374,4 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused"]
+           "make_plan_tiled", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused"]

@@ -129,3 +129,41 @@ def test_steps_with_appends_between_them(torch_cuda, pa, both_schedules):
         return errs
     fused, plain = both_schedules(run)
     assert max(fused) <= TOL and max(plain) <= TOL, (fused, plain)
+
+
+def test_plan_rebuilt_from_arrays_gets_both_schedules(torch_cuda, pa):
+    """C++ callers hand the device plan a decode::DecodePlan they hold as plain arrays
+    (DevicePlan::upload, src/decode/decode.cu:112-156); the layer is recovered from the arrays, so such
+    plans run the head-fused schedule too."""
+    torch = torch_cuda
+    from common import build_cache
+    lens = [2049, 300, 4100, 16, 777]
+    case = Case(FP16, 32, 8, 16, lens, shuffle=1, seed=21)
+    K, V = seeded_kv(case.seq_lens, 8, 128, case.seed)
+    cache, model, cfg = build_cache(case, K, V, torch, pa)
+    q = torch.randn(len(lens), 32, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(12)).cuda()
+    made = pa.make_plan(pa.KVDtype.FP16, lens, 32, 8, 128, 0)
+    rebuilt = pa.plan_from_arrays(made.num_ctas, made.tile, made.segments, made.cta_seg_begin, made.item_seg_begin)
+    before = pa.head_fused()
+    outs = {}
+    try:
+        for name, plan in (("made", made), ("rebuilt", rebuilt)):
+            dp = pa.DevicePlan()
+            dp.upload(plan, 4, 128)
+            for mode in (2, 0):
+                pa.set_head_fused(mode)
+                p = cache.params()
+                out = torch.zeros_like(q)
+                p.q, p.out, p.batch, p.num_q_heads = q.data_ptr(), out.data_ptr(), len(lens), 32
+                dp.bind(p)
+                pa.paged_decode(pa.KVDtype.FP16, p, 0, cfg.num_pages)
+                torch.cuda.synchronize()
+                assert pa.kernel_status() == 0
+                outs[name, mode] = out
+    finally:
+        pa.set_head_fused(before)
+    assert torch.equal(outs["made", 2], outs["rebuilt", 2])
+    assert torch.equal(outs["made", 0], outs["rebuilt", 0])
+    assert not torch.equal(outs["rebuilt", 2], outs["rebuilt", 0]), "the two schedules round differently somewhere"
+    assert (outs["rebuilt", 2].float() - outs["rebuilt", 0].float()).abs().max().item() <= TOL
+    cache.close()
