@@ -119,6 +119,22 @@ int pd_kernel_variant(void);
  * decode call. */
 int pd_set_head_fused(int mode);
 int pd_head_fused(void);
+/* Third knob without a counterpart in the reference: the adaptive cut.  SMs of one GPU do not stream at
+ * the same rate, and CTA c of a grid always runs on the same SM, so with the planner's equal shares the
+ * slower SMs finish tens of microseconds after the others.  While this is on (default; environment
+ * PD_B200_NO_ADAPTIVE=1 switches it off) every decode launch leaves (busy time, tiles) per CTA in a host
+ * table, and pd_device_plan_upload cuts the step, inside the device plan, in shares proportional to the
+ * rates seen so far for that kernel and grid; the plan object a caller holds keeps the reference's equal
+ * cut.  Outputs stay within the path's tolerance but their last bits follow the cut, so a caller that
+ * needs bit-identical results from step to step switches it off.  pd_adaptive_cut_reset forgets the rates. */
+int pd_set_adaptive_cut(int on);
+int pd_adaptive_cut(void);
+int pd_adaptive_cut_reset(void);
+/* Introspection: the index-th rate table (no particular order).  Returns its grid size (0: no such table)
+ * and fills, up to cap CTAs, weights[c] (relative share of CTA c, mean 1) and record[2c], record[2c+1] (total
+ * busy nanoseconds and tiles of CTA c at the last reading), record[2 * grid] launches; either may be NULL,
+ * record needs 2 * cap + 1 entries. */
+int pd_adaptive_cut_table(int index, float* weights, unsigned long long* record, int cap);
 
 /* decode::make_plan (src/decode/decode.hpp:38-39).  num_ctas <= 0 uses
  * pd_default_ctas (needs a GPU).  The plan is a host object; free it with

@@ -63,6 +63,10 @@ SIGNATURES = {
     "pd_default_ctas": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p]),
     "pd_set_kernel_variant": (C.c_int, [C.c_int]),
     "pd_kernel_variant": (C.c_int, []),
+    "pd_set_adaptive_cut": (C.c_int, [C.c_int]),
+    "pd_adaptive_cut": (C.c_int, []),
+    "pd_adaptive_cut_reset": (C.c_int, []),
+    "pd_adaptive_cut_table": (C.c_int, [C.c_int, _vp, _vp, C.c_int]),
     "pd_set_head_fused": (C.c_int, [C.c_int]),
     "pd_head_fused": (C.c_int, []),
     "pd_make_plan": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),

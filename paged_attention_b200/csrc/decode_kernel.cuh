@@ -72,6 +72,19 @@ struct HeadScales {
     const float* v;
 };
 
+// Optional per-CTA record for the host's adaptive cut: every launch adds the CTA's busy nanoseconds to
+// slots[2 * cta] and the tiles it processed to slots[2 * cta + 1], and CTA 0 counts the launch in
+// slots[2 * grid] (one writer per slot, no atomics); the host works with differences between two
+// readings.  Null switches the record off.
+struct CtaStats {
+    unsigned long long* slots;
+};
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 constexpr int MAX_GATHER = 8;
 struct GatherOut {
     int       world;
@@ -534,8 +547,9 @@ __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const int btl_flags /* log2(box tokens) | diagnostic flags */,
                     unsigned* __restrict__ status, const __grid_constant__ GatherOut gp,
-                    const __grid_constant__ HeadScales hs)
+                    const __grid_constant__ HeadScales hs, const __grid_constant__ CtaStats st)
 {
+    const unsigned long long t_entry = (st.slots && threadIdx.x == 0) ? global_ns() : 0ull;
     const int  btl     = btl_flags & 0xff;
     const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
     // diagnostic: use fewer pipeline stages than were allocated (bits 12..15, 0 = all)
@@ -710,6 +724,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     float m_run[2], l_run[2];
     uint32_t qb[8][2];          // Q^T B-fragments for the 8 k-steps
 
+    unsigned tiles_done = 0;
     int c_stage = 0;            // stage of the next tile to consume and the parity of its round
     uint32_t c_phase = 0;
     bool alive = true;
@@ -804,6 +819,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(empty_bar(stage));
             if (++c_stage == nst) { c_stage = 0; c_phase ^= 1; }
+            tiles_done++;
         }
         if (!alive) break;
 
@@ -930,6 +946,11 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 }
             }
         }
+    }
+    if (st.slots && tid == 0) {
+        st.slots[2 * blockIdx.x]     += global_ns() - t_entry;
+        st.slots[2 * blockIdx.x + 1] += tiles_done;
+        if (blockIdx.x == 0) st.slots[2 * gridDim.x] += 1;
     }
     if (gp.world && alive) {
         // Gathered output: this CTA's stores are ordered before its count (device scope); the CTA

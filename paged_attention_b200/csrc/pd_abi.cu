@@ -79,15 +79,16 @@ struct KernelInfo {
     const void* fn;
     int tile, threads, smem, per_sm;
     void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&,
-                   const pdk::HeadScales&, cudaStream_t);
+                   const pdk::HeadScales&, const pdk::CtaStats&, cudaStream_t);
     void (*merge)(const pd_params&, cudaStream_t);
 };
 
 template<typename KV, int GROUP, typename C>
 void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl,
-                   unsigned* status, const pdk::GatherOut& gather, const pdk::HeadScales& scales, cudaStream_t stream) {
+                   unsigned* status, const pdk::GatherOut& gather, const pdk::HeadScales& scales, const pdk::CtaStats& stats,
+                   cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
-    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales);
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales, stats);
 }
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
@@ -154,6 +155,118 @@ const KernelInfo* fused_info(int group) {
 constexpr int FUSED_HEADS = 8;
 constexpr int FUSED_TILE  = 16;
 int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   // 0 never, 1 where it wins, 2 always
+
+// Adaptive cut.  SMs do not stream at the same rate (on B200 groups of SMs are 5-10 % slower than others,
+// stable from launch to launch, and CTA c of a grid always lands on the same SM), so with equal shares the
+// slow SMs finish 20-30 us after the fast ones on a 300 us layer and the tail runs at a fraction of the
+// bandwidth.  Every launch therefore leaves (busy time, tiles) per CTA in a small device table;
+// pd_device_plan_upload queues a copy of it to pinned host memory behind the launches so far, and the
+// upload after that turns the copy into relative rates and cuts the step in shares proportional to them.
+// The caller-visible plan is never changed; the weighted cut is a second schedule inside the device plan.
+bool g_adaptive = std::getenv("PD_B200_NO_ADAPTIVE") == nullptr;
+struct RateTable {
+    int grid = 0;
+    unsigned long long* slots = nullptr;     // device: per CTA running totals (busy ns, tiles), advanced by every launch
+    unsigned long long* host = nullptr;      // pinned copy of an earlier state of `slots`
+    std::vector<unsigned long long> seen;    // the totals the weights already account for
+    cudaEvent_t copied = nullptr;            // completion of the copy into `host`
+    bool copy_queued = false;
+    std::vector<float> weights;              // mean 1; empty until the first usable record
+    int updates = 0;
+};
+struct RateKey {
+    int device; const void* fn; int grid;
+    bool operator==(const RateKey& o) const { return device == o.device && fn == o.fn && grid == o.grid; }
+};
+struct RateKeyHash {
+    size_t operator()(const RateKey& k) const {
+        return std::hash<const void*>()(k.fn) ^ (static_cast<size_t>(k.grid) * 0x9e3779b97f4a7c15ull) ^ static_cast<size_t>(k.device);
+    }
+};
+std::mutex g_rate_mutex;
+std::unordered_map<RateKey, RateTable, RateKeyHash> g_rates;
+
+// The table of (this device, kernel, grid); created on first use.  Pointers into the map stay valid.
+RateTable* rate_table(const void* fn, int grid) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || grid <= 0) return nullptr;
+    std::lock_guard<std::mutex> lock(g_rate_mutex);
+    RateTable& t = g_rates[RateKey{dev, fn, grid}];
+    if (!t.slots) {
+        const size_t bytes = sizeof(unsigned long long) * (2 * grid + 1);   // + launches so far
+        void* dev_mem = nullptr;
+        void* host = nullptr;
+        if (cudaMalloc(&dev_mem, bytes) != cudaSuccess || cudaMemset(dev_mem, 0, bytes) != cudaSuccess ||
+            cudaMallocHost(&host, bytes) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.copied, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(dev_mem);
+            cudaFreeHost(host);
+            g_rates.erase(RateKey{dev, fn, grid});
+            return nullptr;
+        }
+        std::memset(host, 0, bytes);
+        t.slots = static_cast<unsigned long long*>(dev_mem);
+        t.host = static_cast<unsigned long long*>(host);
+        t.seen.assign(2 * static_cast<size_t>(grid) + 1, 0);
+        t.grid = grid;
+    }
+    return &t;
+}
+
+// Folds the latest record into the weights.  Only records of launches long enough that the fixed cost of
+// a CTA (a few microseconds) does not matter are used.
+void update_weights(RateTable* t, cudaStream_t stream) {
+    if (!t) return;
+    std::lock_guard<std::mutex> lock(g_rate_mutex);
+    // Use the copy queued by an earlier upload if it has landed, then queue the next one behind the
+    // launches issued so far.  Nothing here waits for the device.
+    const bool have_copy = t->copy_queued && cudaEventQuery(t->copied) == cudaSuccess;
+    cudaGetLastError();   // cudaErrorNotReady is expected
+    struct Requeue {
+        RateTable* t; cudaStream_t s; bool go;
+        ~Requeue() {
+            if (!go) return;
+            if (cudaMemcpyAsync(t->host, t->slots, sizeof(unsigned long long) * (2 * t->grid + 1), cudaMemcpyDeviceToHost, s) == cudaSuccess &&
+                cudaEventRecord(t->copied, s) == cudaSuccess)
+                t->copy_queued = true;
+            else
+                cudaGetLastError();
+        }
+    } requeue{t, stream, have_copy || !t->copy_queued};
+    if (!have_copy) return;
+    const int n = t->grid;
+    std::vector<double> rate(n, 0.0);
+    double sum = 0.0;
+    int valid = 0;
+    unsigned long long tiles_total = 0;
+    const unsigned long long launches = t->host[2 * n] - t->seen[2 * n];
+    for (int c = 0; c < n; c++) {
+        const double ns = static_cast<double>(t->host[2 * c] - t->seen[2 * c]);
+        const double tiles = static_cast<double>(t->host[2 * c + 1] - t->seen[2 * c + 1]);
+        tiles_total += t->host[2 * c + 1] - t->seen[2 * c + 1];
+        if (ns <= 0.0 || tiles <= 0.0) continue;
+        rate[c] = tiles / ns;
+        sum += rate[c];
+        valid++;
+    }
+    if (launches == 0) return;                             // nothing ran since the last reading
+    t->seen.assign(t->host, t->host + 2 * static_cast<size_t>(n) + 1);
+    // Only launches in which every CTA worked, and for long enough that its few microseconds of ramp-up
+    // and epilogue do not matter (64 tiles are 60-100 us), say something about streaming rates.
+    if (valid < n || tiles_total / launches / n < 64) return;
+    const double mean = sum / valid;
+    if (t->weights.empty()) t->weights.assign(n, 1.0f);
+    const double gain = t->updates < 4 ? 0.5 : 0.3;
+    double wsum = 0.0;
+    for (int c = 0; c < n; c++) {
+        const double target = std::min(1.3, std::max(0.7, rate[c] / mean));
+        t->weights[c] = static_cast<float>((1.0 - gain) * t->weights[c] + gain * target);
+        wsum += t->weights[c];
+    }
+    for (int c = 0; c < n; c++) t->weights[c] = static_cast<float>(t->weights[c] * n / wsum);
+    t->updates++;
+}
 
 template<typename KV>
 const KernelInfo* info_by_variant(int variant, int group) {
@@ -361,6 +474,68 @@ int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int nu
     return PD_OK;
 }
 
+// Where rows are cut in a few pieces (a long batch: 2-3 segments per row) the decode kernel merges
+// them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
+// the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
+int plan_merge_mode(const pd_plan& pl) {
+    static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
+    const int items = static_cast<int>(pl.item_seg_begin.size()) - 1;
+    if (static_cast<int>(pl.segments.size() / 4) <= items) return 0;
+    int widest = 0;
+    for (int i = 0; i < items; i++) widest = std::max(widest, pl.item_seg_begin[i + 1] - pl.item_seg_begin[i]);
+    return (separate_merge || widest > 4) ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
+}
+
+// The planner's cut with unequal shares: CTA c owns the work units [B_c, B_{c+1}) with
+// B_c = round(total * (w_0 + ... + w_{c-1}) / (w_0 + ... + w_{n-1})).  Same segment rules as build_plan.
+int build_plan_weighted(int tile, const int* seq_lens, int batch, int heads, const std::vector<float>& weights, pd_plan** out) {
+    const int grid = static_cast<int>(weights.size());
+    if (tile <= 0 || batch <= 0 || heads <= 0 || grid <= 0) return set_error(PD_INVALID_ARGUMENT, "weighted plan: bad argument");
+    long long total = 0;
+    for (int b = 0; b < batch; b++) {
+        if (seq_lens[b] <= 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: every sequence needs at least one token");
+        total += static_cast<long long>((seq_lens[b] + tile - 1) / tile) * heads;
+    }
+    double wsum = 0.0;
+    for (float w : weights) wsum += w;
+    std::vector<long long> bound(grid + 1, 0);
+    double acc = 0.0;
+    for (int c = 0; c < grid; c++) {
+        acc += weights[c];
+        bound[c + 1] = std::max(bound[c], std::min<long long>(total, std::llround(total * (acc / wsum))));
+    }
+    bound[grid] = total;
+    pd_plan* plan = new pd_plan();
+    plan->tile = tile;
+    plan->num_items = batch * heads;
+    plan->num_ctas = grid;
+    plan->item_seg_begin.assign(plan->num_items + 1, 0);
+    plan->cta_seg_begin.assign(grid + 1, 0);
+    int cta = 0;
+    long long at = 0;                                           // work units before the current item
+    for (int item = 0; item < plan->num_items; item++) {
+        const int b = item / heads, h = item % heads, len = seq_lens[b];
+        const int tiles = (len + tile - 1) / tile;
+        int first = 0;
+        while (first < tiles) {
+            while (bound[cta + 1] <= at + first) {              // this CTA's share is used up: the next one starts here
+                cta++;
+                plan->cta_seg_begin[cta] = static_cast<int>(plan->segments.size() / 4);
+            }
+            const int take = static_cast<int>(std::min<long long>(bound[cta + 1] - (at + first), tiles - first));
+            const int seg[4] = {b, h, first * tile, std::min((first + take) * tile, len)};
+            plan->segments.insert(plan->segments.end(), seg, seg + 4);
+            plan->item_seg_begin[item + 1]++;
+            first += take;
+        }
+        at += tiles;
+    }
+    for (int c = cta + 1; c <= grid; c++) plan->cta_seg_begin[c] = static_cast<int>(plan->segments.size() / 4);
+    for (int i = 0; i < plan->num_items; i++) plan->item_seg_begin[i + 1] += plan->item_seg_begin[i];
+    *out = plan;
+    return PD_OK;
+}
+
 // Host-side validation of a plan against the lengths it was made for; every index
 // the kernels will dereference is checked here so the device never reads out of range.
 int validate_plan(const pd_plan& plan, const int* seq_lens, int batch, int num_kv_heads) {
@@ -414,13 +589,17 @@ struct pd_device_plan {
         const int* cta_seg_begin = nullptr;
         const int* row_seg_begin = nullptr;
         float* partial_out = nullptr;
-    } fused;
+        unsigned long long* stats = nullptr;   // per-CTA record of the launches of this schedule (adaptive cut)
+    } fused,
+      weighted;                    // the caller's (row, kv head) schedule cut in unequal shares (adaptive cut)
+    unsigned long long* stats = nullptr;       // record of launches that run the caller's plan as it is
 };
 
 namespace {
 // Launch-time lookup: standard segment array (what pd_params carries) -> head-fused schedule.
 std::mutex g_fused_mutex;
-std::unordered_map<const void*, pd_device_plan::Fused> g_fused_registry;
+struct AltSchedules { pd_device_plan::Fused fused, weighted; unsigned long long* stats = nullptr; };
+std::unordered_map<const void*, AltSchedules> g_fused_registry;
 }  // namespace
 
 // ---- cache -----------------------------------------------------------------------------------------
@@ -465,6 +644,40 @@ int pd_set_head_fused(int mode) {
     return PD_OK;
 }
 int pd_head_fused(void) { return g_head_fused; }
+
+int pd_set_adaptive_cut(int on) {
+    g_adaptive = on != 0;
+    return PD_OK;
+}
+int pd_adaptive_cut(void) { return g_adaptive ? 1 : 0; }
+// Introspection: the i-th rate table (in no particular order): its grid, weights and latest record.
+// Returns the grid size, 0 when there is no such table.
+int pd_adaptive_cut_table(int index, float* weights, unsigned long long* record, int cap) {
+    std::lock_guard<std::mutex> lock(g_rate_mutex);
+    int i = 0;
+    for (auto& kv : g_rates) {
+        if (i++ != index) continue;
+        const RateTable& t = kv.second;
+        for (int c = 0; c < t.grid && c < cap; c++) {
+            if (weights) weights[c] = t.weights.empty() ? 1.f : t.weights[c];
+            if (record) { record[2 * c] = t.host[2 * c]; record[2 * c + 1] = t.host[2 * c + 1]; }
+        }
+        if (record && t.grid <= cap) record[2 * t.grid] = t.host[2 * t.grid];
+        return t.grid;
+    }
+    return 0;
+}
+int pd_adaptive_cut_reset(void) {
+    std::lock_guard<std::mutex> lock(g_rate_mutex);
+    for (auto& kv : g_rates) {
+        kv.second.weights.clear();
+        kv.second.updates = 0;
+        if (kv.second.copy_queued) cudaEventSynchronize(kv.second.copied);
+        kv.second.copy_queued = false;
+        if (kv.second.host) kv.second.seen.assign(kv.second.host, kv.second.host + 2 * static_cast<size_t>(kv.second.grid) + 1);
+    }
+    return PD_OK;
+}
 
 int pd_set_kernel_variant(int variant) {
     if (variant < 0 || variant >= NUM_VARIANTS) return set_error(PD_INVALID_ARGUMENT, "kernel variant %d does not exist", variant);
@@ -647,7 +860,40 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
             build_plan(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
             rows_plan = nullptr;
     }
-    struct PlanGuard { pd_plan* p; ~PlanGuard() { delete p; } } guard{rows_plan};
+    // Adaptive cut: the schedule that will run (head-fused where it wins, else the caller's) is cut again in
+    // shares proportional to the rates its CTAs showed in earlier launches, once such a record exists.
+    pd_plan* weighted_plan = nullptr;
+    unsigned long long* stats_fused = nullptr;
+    unsigned long long* stats_std = nullptr;
+    const bool fused_runs = rows_plan && g_head_fused != 0 &&
+                            (g_head_fused == 2 || plan_merge_mode(*rows_plan) != pdk::MERGE_SEPARATE);
+    if (g_adaptive && plan->batch > 0 && static_cast<int>(plan->seq_lens.size()) == plan->batch) {
+        if (fused_runs) {
+            RateTable* t = rate_table(fk->fn, rows_plan->num_ctas);
+            update_weights(t, stream);
+            if (t) stats_fused = t->slots;
+            if (t && !t->weights.empty()) {
+                pd_plan* w = nullptr;
+                if (build_plan_weighted(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, t->weights, &w) == PD_OK) {
+                    delete rows_plan;
+                    rows_plan = w;
+                }
+            }
+        } else if (plan->dtype == PD_FP16 || plan->dtype == PD_FP8_E4M3) {
+            const KernelInfo* sk = nullptr;
+            if (find_kernel(plan->dtype, head_dim, group, &sk) == PD_OK && sk->tile == plan->tile && plan->num_ctas > 0 &&
+                plan->num_kv_heads > 0 && plan->num_q_heads / plan->num_kv_heads == group) {
+                RateTable* t = rate_table(sk->fn, plan->num_ctas);
+                update_weights(t, stream);
+                if (t) stats_std = t->slots;
+                if (t && !t->weights.empty() &&
+                    build_plan_weighted(plan->tile, plan->seq_lens.data(), plan->batch, plan->num_kv_heads, t->weights,
+                                        &weighted_plan) != PD_OK)
+                    weighted_plan = nullptr;
+            }
+        }
+    }
+    struct PlanGuard { pd_plan*& p; ~PlanGuard() { delete p; } } guard{rows_plan}, guard_w{weighted_plan};
 
     const size_t seg_bytes  = round16(sizeof(int) * plan->segments.size());
     const size_t cta_bytes  = round16(sizeof(int) * plan->cta_seg_begin.size());
@@ -656,7 +902,11 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     const size_t fseg_bytes = rows_plan ? round16(sizeof(int) * rows_plan->segments.size()) : 0;
     const size_t fcta_bytes = rows_plan ? round16(sizeof(int) * rows_plan->cta_seg_begin.size()) : 0;
     const size_t frow_bytes = rows_plan ? round16(sizeof(int) * rows_plan->item_seg_begin.size()) : 0;
-    const size_t total = std_bytes + fseg_bytes + fcta_bytes + frow_bytes;
+    const size_t alt_bytes  = std_bytes + fseg_bytes + fcta_bytes + frow_bytes;
+    const size_t wseg_bytes = weighted_plan ? round16(sizeof(int) * weighted_plan->segments.size()) : 0;
+    const size_t wcta_bytes = weighted_plan ? round16(sizeof(int) * weighted_plan->cta_seg_begin.size()) : 0;
+    const size_t witm_bytes = weighted_plan ? round16(sizeof(int) * weighted_plan->item_seg_begin.size()) : 0;
+    const size_t total = alt_bytes + wseg_bytes + wcta_bytes + witm_bytes;
     const void* old_key = dp->segments;
     if (total > dp->arena_cap) {
         PD_CUDA(cudaFree(dp->arena));
@@ -682,6 +932,12 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         std::memcpy(h + std_bytes + fseg_bytes + fcta_bytes, rows_plan->item_seg_begin.data(),
                     sizeof(int) * rows_plan->item_seg_begin.size());
     }
+    if (weighted_plan) {
+        std::memcpy(h + alt_bytes, weighted_plan->segments.data(), sizeof(int) * weighted_plan->segments.size());
+        std::memcpy(h + alt_bytes + wseg_bytes, weighted_plan->cta_seg_begin.data(), sizeof(int) * weighted_plan->cta_seg_begin.size());
+        std::memcpy(h + alt_bytes + wseg_bytes + wcta_bytes, weighted_plan->item_seg_begin.data(),
+                    sizeof(int) * weighted_plan->item_seg_begin.size());
+    }
     if (total) PD_CUDA(cudaMemcpyAsync(dp->arena, dp->staging, total, cudaMemcpyHostToDevice, stream));
     PD_CUDA(cudaEventRecord(dp->staged, stream));
 
@@ -692,7 +948,9 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     const size_t std_need = rows * (head_dim + 1) + plan->num_items;
     const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * static_cast<size_t>(group) * FUSED_HEADS : 0;
     const size_t f_need = rows_plan ? frows * (head_dim + 1) + plan->num_items : 0;
-    const size_t need = std_need + f_need;
+    const size_t wrows = weighted_plan ? (weighted_plan->segments.size() / 4) * static_cast<size_t>(group) : 0;
+    const size_t w_need = weighted_plan ? wrows * (head_dim + 1) + plan->num_items : 0;
+    const size_t need = std_need + f_need + w_need;
     if (need > dp->partial_cap) {
         PD_CUDA(cudaFree(dp->partial));
         dp->partial = nullptr; dp->partial_cap = 0;
@@ -712,15 +970,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // Where rows are cut in a few pieces (a long batch: 2-3 segments per row) the decode kernel merges
     // them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
     // the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
-    static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
-    auto merge_mode = [&](const pd_plan& pl) {
-        const int items = static_cast<int>(pl.item_seg_begin.size()) - 1;
-        if (static_cast<int>(pl.segments.size() / 4) <= items) return 0;
-        int widest = 0;
-        for (int i = 0; i < items; i++) widest = std::max(widest, pl.item_seg_begin[i + 1] - pl.item_seg_begin[i]);
-        return (separate_merge || widest > 4) ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
-    };
-    dp->needs_merge = merge_mode(*plan);
+    dp->needs_merge = plan_merge_mode(*plan);
     if (plan->num_items)
         PD_CUDA(cudaMemsetAsync(dp->partial + rows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
 
@@ -731,7 +981,8 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         f.dtype = plan->dtype; f.group = group; f.batch = plan->batch;
         f.num_ctas = rows_plan->num_ctas;
         f.num_segments = static_cast<int>(rows_plan->segments.size() / 4);
-        f.needs_merge = merge_mode(*rows_plan);
+        f.needs_merge = plan_merge_mode(*rows_plan);
+        f.stats = stats_fused;
         f.rows = frows;
         f.segments = a + std_bytes;
         f.cta_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes);
@@ -739,10 +990,28 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         f.partial_out = dp->partial + std_need;
         PD_CUDA(cudaMemsetAsync(f.partial_out + frows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     }
+    dp->weighted = pd_device_plan::Fused{};
+    dp->stats = stats_std;
+    if (weighted_plan) {
+        auto& f = dp->weighted;
+        f.valid = true;
+        f.dtype = plan->dtype; f.group = group; f.batch = plan->batch;
+        f.num_ctas = weighted_plan->num_ctas;
+        f.num_segments = static_cast<int>(weighted_plan->segments.size() / 4);
+        f.needs_merge = plan_merge_mode(*weighted_plan);
+        f.rows = wrows;
+        f.segments = a + alt_bytes;
+        f.cta_seg_begin = reinterpret_cast<const int*>(a + alt_bytes + wseg_bytes);
+        f.row_seg_begin = reinterpret_cast<const int*>(a + alt_bytes + wseg_bytes + wcta_bytes);   // (row, kv head) items
+        f.partial_out = dp->partial + std_need + f_need;
+        f.stats = stats_std;
+        PD_CUDA(cudaMemsetAsync(f.partial_out + wrows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
+    }
     {
         std::lock_guard<std::mutex> lock(g_fused_mutex);
         if (old_key) g_fused_registry.erase(old_key);
-        if (dp->fused.valid) g_fused_registry[dp->segments] = dp->fused;
+        if (dp->fused.valid || dp->weighted.valid || dp->stats)
+            g_fused_registry[dp->segments] = AltSchedules{dp->fused, dp->weighted, dp->stats};
         else g_fused_registry.erase(dp->segments);
     }
     return PD_OK;
@@ -803,6 +1072,8 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     dp->built_on_device = true;
     dp->tile            = k->tile;
     dp->fused           = pd_device_plan::Fused{};
+    dp->weighted        = pd_device_plan::Fused{};
+    dp->stats           = nullptr;
     {
         std::lock_guard<std::mutex> lock(g_fused_mutex);
         if (old_key) g_fused_registry.erase(old_key);
@@ -900,34 +1171,42 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     }
     const bool skip_merge = p->needs_merge < 0;
     int box_heads = 1;
-    if (g_head_fused && p->num_kv_heads == FUSED_HEADS) {
-        pd_device_plan::Fused f;
+    unsigned long long* stats_slots = nullptr;
+    {
+        AltSchedules alt;
         bool found = false;
         {
             std::lock_guard<std::mutex> lock(g_fused_mutex);
             auto it = g_fused_registry.find(p->segments);
-            if (it != g_fused_registry.end()) { f = it->second; found = true; }
+            if (it != g_fused_registry.end()) { alt = it->second; found = true; }
         }
-        const KernelInfo* fk = dtype == PD_FP16 ? fused_info<__half>(p->num_q_heads / p->num_kv_heads) : nullptr;
-        // Mode 1 keeps the (row, kv head) schedule where rows would be spread over more than 4 CTAs each.
-        const bool wins = g_head_fused == 2 || f.needs_merge != pdk::MERGE_SEPARATE;
-        if (found && fk && wins && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch &&
-            f.group == p->num_q_heads / p->num_kv_heads) {
+        const int group = p->num_q_heads / p->num_kv_heads;
+        auto matches = [&](const pd_device_plan::Fused& f) {
+            return f.valid && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch && f.group == group;
+        };
+        const KernelInfo* fk = dtype == PD_FP16 && p->num_kv_heads == FUSED_HEADS ? fused_info<__half>(group) : nullptr;
+        // Head-fused, mode 1: not where rows would be spread over more than 4 CTAs each.
+        const bool use_fused = found && fk && g_head_fused && matches(alt.fused) &&
+                               (g_head_fused == 2 || alt.fused.needs_merge != pdk::MERGE_SEPARATE);
+        const bool use_weighted = found && !use_fused && g_adaptive && matches(alt.weighted);
+        if (found && g_adaptive && !use_fused && !use_weighted) stats_slots = alt.stats;
+        if (use_fused || use_weighted) {
+            const pd_device_plan::Fused& f = use_fused ? alt.fused : alt.weighted;
             fused_params = *p;
             fused_params.segments = f.segments;
             fused_params.cta_seg_begin = f.cta_seg_begin;
-            fused_params.item_seg_begin = f.row_seg_begin;       // work items are rows
+            fused_params.item_seg_begin = f.row_seg_begin;       // work items: rows (head-fused) or (row, kv head)
             fused_params.num_ctas = f.num_ctas;
-            fused_params.needs_merge = p->needs_merge < 0 ? 0 : f.needs_merge;   // the row schedule has its own splits
+            fused_params.needs_merge = p->needs_merge < 0 ? 0 : f.needs_merge;   // this schedule has its own splits
             if (gather.world && fused_params.needs_merge) fused_params.needs_merge = pdk::MERGE_IN_KERNEL;   // gathered rows are written by the decode kernel
             fused_params.partial_out = f.partial_out;
             fused_params.partial_lse = f.partial_out + f.rows * p->head_dim;
             p = &fused_params;
-            k = fk;
-            box_heads = FUSED_HEADS;
+            if (use_fused) { k = fk; box_heads = FUSED_HEADS; }
+            if (g_adaptive) stats_slots = f.stats;
         }
     }
-    if (skip_merge && box_heads == 1) p = &unmerged;
+    if (skip_merge && p != &fused_params) p = &unmerged;
     if (int rc = configure(k)) return rc;
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -946,7 +1225,7 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     static const int stage_limit = std::getenv("PD_B200_STAGE_LIMIT") ? (std::atoi(std::getenv("PD_B200_STAGE_LIMIT")) & 0xf) : 0;
     k->launch(*p, k_map, v_map,
               btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
-              status, gather, scales, stream);
+              status, gather, scales, pdk::CtaStats{stats_slots}, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, stream);
@@ -1063,7 +1342,8 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, pdk::HeadScales{nullptr, nullptr}, stream);
+    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, pdk::HeadScales{nullptr, nullptr},
+              pdk::CtaStats{nullptr}, stream);
     PD_CUDA(cudaGetLastError());
     if (local.needs_merge) {
         k->merge(local, stream);

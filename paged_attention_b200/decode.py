@@ -79,6 +79,34 @@ def head_fused():
     return int(_lib.lib().pd_head_fused())
 
 
+def set_adaptive_cut(on):
+    """Adaptive cut (not in the reference): device plans are cut in shares proportional to the streaming
+    rate each CTA showed in earlier launches.  On by default."""
+    check(_lib.lib().pd_set_adaptive_cut(int(bool(on))))
+
+
+def adaptive_cut():
+    return bool(_lib.lib().pd_adaptive_cut())
+
+
+def adaptive_cut_reset():
+    """Forget the rates learned so far."""
+    check(_lib.lib().pd_adaptive_cut_reset())
+
+
+def adaptive_cut_tables():
+    """[(weights, launches)] of every (kernel, grid) the adaptive cut has seen: relative share per CTA."""
+    out = []
+    for index in range(1 << 16):
+        w = np.zeros(4096, np.float32)
+        r = np.zeros(2 * 4096 + 1, np.uint64)
+        n = _lib.lib().pd_adaptive_cut_table(index, w.ctypes.data, r.ctypes.data, 4096)
+        if n <= 0:
+            break
+        out.append((w[:min(n, 4096)].copy(), int(r[2 * n]) if n <= 4096 else 0))
+    return out
+
+
 class DecodePlan:
     """decode::DecodePlan (src/decode/decode.hpp:21-27). Owns (or borrows) a pd_plan handle."""
 
@@ -374,4 +402,5 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused"]
+           "make_plan_tiled", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused",
+           "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_tables"]

@@ -28,3 +28,18 @@ def pa():
     """The engine's Python mirror; building the library is the job of __graft_entry__.build()."""
     import paged_attention_b200
     return paged_attention_b200
+
+
+@pytest.fixture(autouse=True)
+def fixed_cut(request):
+    """Most tests compare outputs bit for bit between entry points or between steps, so they run with the
+    adaptive cut (shares that follow measured per-CTA rates) switched off; tests of the adaptive cut itself
+    switch it on."""
+    if "pa" not in request.fixturenames:
+        yield
+        return
+    pa = request.getfixturevalue("pa")
+    before = pa.adaptive_cut()
+    pa.set_adaptive_cut(False)
+    yield
+    pa.set_adaptive_cut(before)
