@@ -147,6 +147,12 @@ int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int
  * reference's published (ctas, segments) pairs, which were made at tile 64. */
 int pd_make_plan_tiled(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
                        int num_ctas, pd_plan** out);
+/* The planner's segment rules with unequal shares (no counterpart in the reference): CTA c owns the work
+ * units [B_c, B_c+1), B_c = round(total * (w_0 + .. + w_c-1) / sum(w)).  This is the cut the adaptive
+ * schedule uses inside the device plan; exposed so that it can be checked on the host.  Pure host
+ * arithmetic. */
+int pd_make_plan_weighted(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                          const float* weights, int num_ctas, pd_plan** out);
 /* A plan object from arrays the caller already holds: a decode::DecodePlan filled in by
  * the caller (src/decode/decode.hpp:21-27 is a plain struct that callers may build or edit
  * themselves before DevicePlan::upload).  The tables are checked for consistency

@@ -71,6 +71,7 @@ SIGNATURES = {
     "pd_head_fused": (C.c_int, []),
     "pd_make_plan": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "pd_make_plan_tiled": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
+    "pd_make_plan_weighted": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, _vp, C.c_int, C.POINTER(_vp)]),
     "pd_plan_from_arrays": (C.c_int, [C.c_int, C.c_int, _i32p, C.c_int, _i32p, _i32p, C.c_int, C.POINTER(_vp)]),
     "pd_plan_free": (None, [_vp]),
     "pd_plan_num_ctas": (C.c_int, [_vp]),

@@ -744,6 +744,21 @@ int pd_make_plan(int dtype, const int* seq_lens, int batch, int num_q_heads, int
     return PD_OK;
 }
 
+int pd_make_plan_weighted(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads,
+                          const float* weights, int num_ctas, pd_plan** out) {
+    if (!out || !weights || (batch > 0 && !seq_lens)) return set_error(PD_INVALID_ARGUMENT, "make_plan_weighted: null argument");
+    if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    if (num_ctas <= 0 || batch <= 0) return set_error(PD_INVALID_ARGUMENT, "make_plan_weighted: batch and num_ctas must be positive");
+    double sum = 0.0;
+    for (int c = 0; c < num_ctas; c++) {
+        if (!(weights[c] >= 0.f)) return set_error(PD_INVALID_ARGUMENT, "make_plan_weighted: weights must not be negative");
+        sum += weights[c];
+    }
+    if (!(sum > 0.0)) return set_error(PD_INVALID_ARGUMENT, "make_plan_weighted: some weight must be positive");
+    return build_plan_weighted(tile, seq_lens, batch, num_kv_heads, std::vector<float>(weights, weights + num_ctas), out);
+}
+
 int pd_plan_from_arrays(int num_ctas, int tile, const int* segments, int num_segments, const int* cta_seg_begin,
                         const int* item_seg_begin, int num_items, pd_plan** out) {
     if (!out || num_ctas < 0 || tile <= 0 || num_segments < 0 || num_items < 0 || !cta_seg_begin || !item_seg_begin ||

@@ -161,6 +161,15 @@ def make_plan(dtype, seq_lens, num_q_heads, num_kv_heads, head_dim, num_ctas=0):
     return DecodePlan(h)
 
 
+def make_plan_weighted(tile, seq_lens, num_q_heads, num_kv_heads, weights):
+    """The planner with one relative share per CTA (the cut of the adaptive schedule); host arithmetic only."""
+    lens, p = _lens_arg(seq_lens)
+    w = np.ascontiguousarray(weights, dtype=np.float32)
+    h = C.c_void_p()
+    check(_lib.lib().pd_make_plan_weighted(tile, p, len(lens), num_q_heads, num_kv_heads, w.ctypes.data, len(w), C.byref(h)))
+    return DecodePlan(h)
+
+
 def plan_from_arrays(num_ctas, tile, segments, cta_seg_begin, item_seg_begin):
     """A DecodePlan from the arrays of a decode::DecodePlan made elsewhere (src/decode/decode.hpp:21-27),
     e.g. by the reference's own planner; the tables are checked for consistency."""
@@ -402,5 +411,5 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused",
+           "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused",
            "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_tables"]

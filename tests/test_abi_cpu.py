@@ -148,3 +148,53 @@ def test_product_does_not_reach_for_the_oracle():
                 with open(os.path.join(dirpath, f)) as fh:
                     text = fh.read()
                 assert "oracle" not in text.lower() or f == "build.py", f"{f} mentions the oracle"
+
+
+def _check_cover(plan, lens, hkv, tile):
+    """Every (row, kv head) is covered from 0 to its length by consecutive segments, in item order, and the
+    CTA table walks the segment array without gaps."""
+    seg, item, cta = plan.segments, plan.item_seg_begin, plan.cta_seg_begin
+    assert item[0] == 0 and item[-1] == len(seg) and cta[0] == 0 and cta[-1] == len(seg)
+    assert (np.diff(cta) >= 0).all() and (np.diff(item) >= 1).all()
+    for i in range(len(lens) * hkv):
+        b, h = divmod(i, hkv)
+        at = 0
+        for s in seg[item[i]:item[i + 1]]:
+            assert (s[0], s[1], s[2]) == (b, h, at) and s[2] % tile == 0 and s[3] > s[2]
+            at = s[3]
+        assert at == lens[b]
+
+
+def test_weighted_planner_shares_follow_the_weights(pa):
+    rng = np.random.default_rng(5)
+    for _ in range(30):
+        tile = int(rng.choice([16, 64]))
+        hkv = int(rng.choice([1, 2, 8]))
+        lens = rng.integers(1, 9000, int(rng.integers(1, 80))).tolist()
+        grid = int(rng.choice([1, 7, 148, 296, 443]))
+        w = rng.uniform(0.7, 1.3, grid).astype(np.float32)
+        plan = pa.make_plan_weighted(tile, lens, hkv * 4, hkv, w)
+        assert plan.num_ctas == grid and plan.tile == tile
+        _check_cover(plan, lens, hkv, tile)
+        # tiles per CTA against the ideal share: off by less than one tile at each end
+        tiles = np.zeros(grid)
+        seg, cta = plan.segments, plan.cta_seg_begin
+        for c in range(grid):
+            for s in seg[cta[c]:cta[c + 1]]:
+                tiles[c] += -(-(s[3] - s[2]) // tile)
+        total = sum(-(-n // tile) for n in lens) * hkv
+        assert tiles.sum() == total
+        assert np.abs(tiles - total * w.astype(np.float64) / w.astype(np.float64).sum()).max() <= 1.0 + 1e-6
+    # a CTA with weight 0 gets nothing and the rest still cover everything
+    plan = pa.make_plan_weighted(64, [5000, 300], 32, 8, [1, 0, 1, 0, 0, 2])
+    _check_cover(plan, [5000, 300], 8, 64)
+    cta = plan.cta_seg_begin
+    assert cta[1] == cta[2] and cta[3] == cta[4] == cta[5]
+    with pytest.raises(pa.InvalidArgument):
+        pa.make_plan_weighted(64, [10], 32, 8, [1.0, -1.0])
+
+
+def test_equal_cut_covers_like_the_weighted_one(pa):
+    lens = [8192] * 5 + [17]
+    plan = pa.make_plan_tiled(64, lens, 32, 8, 296)
+    _check_cover(plan, lens, 8, 64)
