@@ -962,18 +962,22 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 }
 
 // ---- merge kernel -------------------------------------------------------------------
-// One warp per (row, query head) whose (row, kv head) was split.  Lanes first run
-// over the segments (max and sum of the base-2 LSE weights by butterfly shuffles),
-// then over the head dimension, four floats per lane, with each segment's weight
-// broadcast by shuffle.  Same arithmetic as merge_segments_kernel
-// (src/decode/decode_kernels.cuh:409-432).
+// One CTA of four warps per (row, query head) whose (row, kv head) was split.
+// Up to MERGE_WIDE_MIN pieces: warp 0 alone, lanes first over the segments (max and sum of the base-2
+// LSE weights by butterfly shuffles), then over the head dimension, four floats per lane, with each
+// segment's weight broadcast by shuffle: the arithmetic of merge_segments_kernel
+// (src/decode/decode_kernels.cuh:409-432), in the order the decode kernel's own merge uses, so both give
+// the same bits.  More pieces (one long sequence spread over the whole grid: dozens per row): the four
+// warps take every fourth piece each, four loads in flight per warp, and add up through shared memory;
+// with one warp per (row, head) such a merge was a third of a single-sequence decode step.
 // ROW_ITEMS = true: the plan's work items are rows (head-fused tiles).
+constexpr int MERGE_WIDE_MIN = 8;
 template<int GROUP, bool ROW_ITEMS = false>
 __global__ void __launch_bounds__(128)
 merge_segments_kernel(const __grid_constant__ pd_params p)
 {
-    const int lane = threadIdx.x & 31;
-    const int idx  = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (row, q head)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int idx  = blockIdx.x;                                            // (row, q head)
     if (idx >= p.batch * p.num_q_heads) return;
     const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
     const int item = ROW_ITEMS ? b : b * p.num_kv_heads + hq / GROUP;
@@ -981,8 +985,55 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
     if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) return;   // merged by the decode kernel
     GatherOut local{};   // world = 0: plain output
-    if (ROW_ITEMS) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, p.num_q_heads, hq);
-    else           merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, GROUP, hq % GROUP);
+    const int stride = ROW_ITEMS ? p.num_q_heads : GROUP;
+    const int gq     = ROW_ITEMS ? hq : hq % GROUP;
+    if (s1 - s0 <= MERGE_WIDE_MIN) {
+        if (warp == 0) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, stride, gq);
+        return;
+    }
+    __shared__ float4 part_num[4][32];
+    __shared__ float  part_den[4];
+    float lse_max = -INFINITY;
+    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * stride + gq));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (int base = s0 + warp; base < s1; base += 16) {
+        float  w[4];
+        float4 o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int s = base + 4 * j;
+            const bool live = s < s1;
+            w[j] = live ? exp2f(__ldcg(p.partial_lse + s * stride + gq) - lse_max) : 0.f;
+            o[j] = live ? __ldcg(reinterpret_cast<const float4*>(
+                              p.partial_out + (static_cast<size_t>(s) * stride + gq) * HEAD_DIM + lane * 4))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            num.x = fmaf(w[j], o[j].x, num.x); num.y = fmaf(w[j], o[j].y, num.y);
+            num.z = fmaf(w[j], o[j].z, num.z); num.w = fmaf(w[j], o[j].w, num.w);
+            den += w[j];
+        }
+    }
+    part_num[warp][lane] = num;
+    if (lane == 0) part_den[warp] = den;
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 1; w < 4; w++) {
+        const float4 other = part_num[w][lane];
+        num.x += other.x; num.y += other.y; num.z += other.z; num.w += other.w;
+        den += part_den[w];
+    }
+    const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
+    const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    store_out(p, local, out_index(p, local, b, hq) + lane * 4, packed);
 }
 
 // Waits (bounded) until every peer's flag has reached `epoch`: their slices are in this GPU's

@@ -93,7 +93,7 @@ void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap&
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
     const int rows = p.batch * p.num_q_heads;
-    pdk::merge_segments_kernel<GROUP><<<(rows + 3) / 4, 128, 0, stream>>>(p);
+    pdk::merge_segments_kernel<GROUP><<<rows, 128, 0, stream>>>(p);
 }
 
 template<typename KV, int GROUP, int V>
@@ -129,7 +129,7 @@ template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>;
 template<int GROUP>
 void launch_merge_rows(const pd_params& p, cudaStream_t stream) {
     const int rows = p.batch * p.num_q_heads;
-    pdk::merge_segments_kernel<GROUP, true><<<(rows + 3) / 4, 128, 0, stream>>>(p);
+    pdk::merge_segments_kernel<GROUP, true><<<rows, 128, 0, stream>>>(p);
 }
 
 template<typename KV, int GROUP>
