@@ -570,6 +570,9 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     auto empty_bar = [&](int s) { return bars + (STAGES + s) * 8; };
     const uint32_t sync_bar = bars + 2 * STAGES * 8;   // consumer-warp rendezvous (bounded, unlike bar.sync)
 
+    // Let a dependent launch (the merge kernel) be scheduled as soon as SMs have room; it waits for this
+    // whole grid before it reads anything this grid writes.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int seg_begin = p.cta_seg_begin[blockIdx.x];
     const int seg_end   = p.cta_seg_begin[blockIdx.x + 1];
     if (seg_begin >= seg_end) {
@@ -981,7 +984,10 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     if (idx >= p.batch * p.num_q_heads) return;
     const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
     const int item = ROW_ITEMS ? b : b * p.num_kv_heads + hq / GROUP;
-    const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];
+    const int s0 = p.item_seg_begin[item], s1 = p.item_seg_begin[item + 1];   // plan data: not written by the decode kernel
+    // Launched as a programmatic dependent of the decode kernel: the CTAs may already be resident while
+    // the decode kernel drains; everything below reads what that kernel wrote, so wait for it here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
     if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) return;   // merged by the decode kernel
     GatherOut local{};   // world = 0: plain output

@@ -90,10 +90,25 @@ void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap&
     using S = pdk::Shape<KV, GROUP, C>;
     pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales, stats);
 }
+// The merge kernel is launched as a programmatic dependent of the decode kernel before it: its CTAs are
+// placed while the decode grid drains and wait inside the kernel (griddepcontrol.wait) until that grid is
+// complete, which takes the launch latency out of the gap between the two kernels.
+template<typename Kernel>
+void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, p);
+}
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
-    const int rows = p.batch * p.num_q_heads;
-    pdk::merge_segments_kernel<GROUP><<<rows, 128, 0, stream>>>(p);
+    launch_dependent(pdk::merge_segments_kernel<GROUP, false>, p.batch * p.num_q_heads, p, stream);
 }
 
 template<typename KV, int GROUP, int V>
@@ -128,8 +143,7 @@ template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>;
 
 template<int GROUP>
 void launch_merge_rows(const pd_params& p, cudaStream_t stream) {
-    const int rows = p.batch * p.num_q_heads;
-    pdk::merge_segments_kernel<GROUP, true><<<rows, 128, 0, stream>>>(p);
+    launch_dependent(pdk::merge_segments_kernel<GROUP, true>, p.batch * p.num_q_heads, p, stream);
 }
 
 template<typename KV, int GROUP>
