@@ -186,9 +186,11 @@ int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
  * largest batch it allocates nothing and may be captured into a CUDA graph together with the decode that
  * follows.  num_ctas <= 0: pd_default_ctas.  The launch grid is num_ctas; CTAs the cut does not need idle.
  * pd_device_plan_bind then sets needs_merge = 3: rows cut in at most 4 pieces are merged inside the decode
- * kernel, the others by the merge kernel, which is always launched (the host cannot know).  Rows are
- * always scheduled by (row, kv head).  A length <= 0 gives that row no work and is reported by
- * pd_device_plan_info (the host planner refuses such a batch).
+ * kernel, the others by the merge kernel, which is always launched (the host cannot know).  For fp16
+ * layers with 8 kv heads and at least a third as many rows as the one-CTA-per-SM grid has CTAs, a second
+ * launch of the same planner also cuts the step by rows for the head-fused schedule (pd_set_head_fused).
+ * The adaptive cut does not apply to plans cut on the device.  A length <= 0 gives that row no work and
+ * is reported by pd_device_plan_info (the host planner refuses such a batch).
  * pd_device_plan_info (waits for the stream): out[0] CTAs with work, out[1] segments, out[2] most pieces
  * any (row, kv head) was cut in, out[3] 1 + first row with a length <= 0 (0: none).
  * pd_device_plan_fetch (waits for the stream): the plan as a host object, for inspection and tests. */

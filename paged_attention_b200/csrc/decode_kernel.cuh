@@ -864,7 +864,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                             p.partial_lse[static_cast<size_t>(seg) * p.num_q_heads + hq] = m_run[h] + log2f(l[h]);
                     }
                 }
-                if (!whole_row && p.needs_merge == MERGE_IN_KERNEL) {
+                if (!whole_row && (p.needs_merge == MERGE_IN_KERNEL ||
+                                   (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES))) {
                     // one arrival counter per (row, kv head); the warp that completes it merges the head's group
                     int* counter = reinterpret_cast<int*>(p.partial_lse + static_cast<size_t>(p.cta_seg_begin[p.num_ctas]) * p.num_q_heads)
                                    + sg.x * S::HEADS + warp;

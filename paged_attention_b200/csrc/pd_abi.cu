@@ -170,116 +170,9 @@ constexpr int FUSED_HEADS = 8;
 constexpr int FUSED_TILE  = 16;
 int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   // 0 never, 1 where it wins, 2 always
 
-// Adaptive cut.  SMs do not stream at the same rate (on B200 groups of SMs are 5-10 % slower than others,
-// stable from launch to launch, and CTA c of a grid always lands on the same SM), so with equal shares the
-// slow SMs finish 20-30 us after the fast ones on a 300 us layer and the tail runs at a fraction of the
-// bandwidth.  Every launch therefore leaves (busy time, tiles) per CTA in a small device table;
-// pd_device_plan_upload queues a copy of it to pinned host memory behind the launches so far, and the
-// upload after that turns the copy into relative rates and cuts the step in shares proportional to them.
-// The caller-visible plan is never changed; the weighted cut is a second schedule inside the device plan.
-bool g_adaptive = std::getenv("PD_B200_NO_ADAPTIVE") == nullptr;
-struct RateTable {
-    int grid = 0;
-    unsigned long long* slots = nullptr;     // device: per CTA running totals (busy ns, tiles), advanced by every launch
-    unsigned long long* host = nullptr;      // pinned copy of an earlier state of `slots`
-    std::vector<unsigned long long> seen;    // the totals the weights already account for
-    cudaEvent_t copied = nullptr;            // completion of the copy into `host`
-    bool copy_queued = false;
-    std::vector<float> weights;              // mean 1; empty until the first usable record
-    int updates = 0;
-};
-struct RateKey {
-    int device; const void* fn; int grid;
-    bool operator==(const RateKey& o) const { return device == o.device && fn == o.fn && grid == o.grid; }
-};
-struct RateKeyHash {
-    size_t operator()(const RateKey& k) const {
-        return std::hash<const void*>()(k.fn) ^ (static_cast<size_t>(k.grid) * 0x9e3779b97f4a7c15ull) ^ static_cast<size_t>(k.device);
-    }
-};
-std::mutex g_rate_mutex;
-std::unordered_map<RateKey, RateTable, RateKeyHash> g_rates;
-
-// The table of (this device, kernel, grid); created on first use.  Pointers into the map stay valid.
-RateTable* rate_table(const void* fn, int grid) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || grid <= 0) return nullptr;
-    std::lock_guard<std::mutex> lock(g_rate_mutex);
-    RateTable& t = g_rates[RateKey{dev, fn, grid}];
-    if (!t.slots) {
-        const size_t bytes = sizeof(unsigned long long) * (2 * grid + 1);   // + launches so far
-        void* dev_mem = nullptr;
-        void* host = nullptr;
-        if (cudaMalloc(&dev_mem, bytes) != cudaSuccess || cudaMemset(dev_mem, 0, bytes) != cudaSuccess ||
-            cudaMallocHost(&host, bytes) != cudaSuccess ||
-            cudaEventCreateWithFlags(&t.copied, cudaEventDisableTiming) != cudaSuccess) {
-            cudaGetLastError();
-            cudaFree(dev_mem);
-            cudaFreeHost(host);
-            g_rates.erase(RateKey{dev, fn, grid});
-            return nullptr;
-        }
-        std::memset(host, 0, bytes);
-        t.slots = static_cast<unsigned long long*>(dev_mem);
-        t.host = static_cast<unsigned long long*>(host);
-        t.seen.assign(2 * static_cast<size_t>(grid) + 1, 0);
-        t.grid = grid;
-    }
-    return &t;
-}
-
-// Folds the latest record into the weights.  Only records of launches long enough that the fixed cost of
-// a CTA (a few microseconds) does not matter are used.
-void update_weights(RateTable* t, cudaStream_t stream) {
-    if (!t) return;
-    std::lock_guard<std::mutex> lock(g_rate_mutex);
-    // Use the copy queued by an earlier upload if it has landed, then queue the next one behind the
-    // launches issued so far.  Nothing here waits for the device.
-    const bool have_copy = t->copy_queued && cudaEventQuery(t->copied) == cudaSuccess;
-    cudaGetLastError();   // cudaErrorNotReady is expected
-    struct Requeue {
-        RateTable* t; cudaStream_t s; bool go;
-        ~Requeue() {
-            if (!go) return;
-            if (cudaMemcpyAsync(t->host, t->slots, sizeof(unsigned long long) * (2 * t->grid + 1), cudaMemcpyDeviceToHost, s) == cudaSuccess &&
-                cudaEventRecord(t->copied, s) == cudaSuccess)
-                t->copy_queued = true;
-            else
-                cudaGetLastError();
-        }
-    } requeue{t, stream, have_copy || !t->copy_queued};
-    if (!have_copy) return;
-    const int n = t->grid;
-    std::vector<double> rate(n, 0.0);
-    double sum = 0.0, busy_total = 0.0;
-    int valid = 0;
-    const unsigned long long launches = t->host[2 * n] - t->seen[2 * n];
-    for (int c = 0; c < n; c++) {
-        const double ns = static_cast<double>(t->host[2 * c] - t->seen[2 * c]);
-        const double tiles = static_cast<double>(t->host[2 * c + 1] - t->seen[2 * c + 1]);
-        busy_total += ns;
-        if (ns <= 0.0 || tiles <= 0.0) continue;
-        rate[c] = tiles / ns;
-        sum += rate[c];
-        valid++;
-    }
-    if (launches == 0) return;                             // nothing ran since the last reading
-    t->seen.assign(t->host, t->host + 2 * static_cast<size_t>(n) + 1);
-    // Only launches in which every CTA worked, and for long enough (120 us on average) that its few
-    // microseconds of ramp-up and epilogue do not matter, say something about streaming rates.
-    if (valid < n || busy_total / static_cast<double>(launches) / n < 120000.0) return;
-    const double mean = sum / valid;
-    if (t->weights.empty()) t->weights.assign(n, 1.0f);
-    const double gain = t->updates < 4 ? 0.5 : 0.3;
-    double wsum = 0.0;
-    for (int c = 0; c < n; c++) {
-        const double target = std::min(1.3, std::max(0.7, rate[c] / mean));
-        t->weights[c] = static_cast<float>((1.0 - gain) * t->weights[c] + gain * target);
-        wsum += t->weights[c];
-    }
-    for (int c = 0; c < n; c++) t->weights[c] = static_cast<float>(t->weights[c] * n / wsum);
-    t->updates++;
-}
+}  // namespace
+#include "adaptive_cut.hpp"
+namespace {
 
 template<typename KV>
 const KernelInfo* info_by_variant(int variant, int group) {
@@ -409,164 +302,8 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
     return PD_OK;
 }
 
-// ---- planner ------------------------------------------------------------------------------
-
-// The flat list of (row, kv head, tile) work units is cut into num_ctas contiguous
-// runs of `per` units; each maximal run of one (row, head) inside a CTA's share is a
-// segment.  Produces exactly the plan of decode::make_plan (src/decode/decode.cu:65-108)
-// for the same tile and num_ctas.
-int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads, int num_ctas,
-               pd_plan** out);
-
 }  // namespace
-
-struct pd_plan {
-    int num_ctas = 0;
-    int tile     = 0;
-    int num_items = 0;
-    std::vector<int> segments;        // 4 ints each
-    std::vector<int> cta_seg_begin;
-    std::vector<int> item_seg_begin;
-    // what pd_make_plan knew when it cut the plan (dtype < 0: unknown, e.g. built from arrays); lets the
-    // device plan also carry the head-fused schedule of the same step
-    int dtype = -1, batch = 0, num_q_heads = 0, num_kv_heads = 0, forced_ctas = 0;
-    std::vector<int> seq_lens;
-};
-
-namespace {
-
-int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int num_kv_heads, int num_ctas,
-               pd_plan** out) {
-    if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads != 0)
-        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
-    if (tile <= 0 || num_ctas <= 0 || batch < 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: tile, num_ctas must be positive");
-    long long total = 0;
-    for (int b = 0; b < batch; b++) {
-        if (seq_lens[b] <= 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: every sequence needs at least one token");
-        total += static_cast<long long>((seq_lens[b] + tile - 1) / tile) * num_kv_heads;
-    }
-    pd_plan* plan = new pd_plan();
-    plan->tile = tile;
-    plan->num_items = batch * num_kv_heads;
-    plan->item_seg_begin.assign(plan->num_items + 1, 0);
-    if (total == 0) {   // empty batch: nothing to launch
-        plan->cta_seg_begin.assign(1, 0);
-        *out = plan;
-        return PD_OK;
-    }
-    const long long per = (total + num_ctas - 1) / num_ctas;   // work units per CTA
-    plan->num_ctas = static_cast<int>((total + per - 1) / per);
-    plan->cta_seg_begin.reserve(plan->num_ctas + 1);
-    plan->cta_seg_begin.push_back(0);
-    long long room = per;                                      // units the current CTA can still take
-    for (int item = 0; item < plan->num_items; item++) {
-        const int b = item / num_kv_heads, h = item % num_kv_heads;
-        const int len = seq_lens[b];
-        const int tiles = (len + tile - 1) / tile;
-        int first = 0;
-        while (first < tiles) {
-            if (room == 0) {
-                plan->cta_seg_begin.push_back(static_cast<int>(plan->segments.size() / 4));
-                room = per;
-            }
-            const int take = static_cast<int>(std::min<long long>(room, tiles - first));
-            const int seg[4] = {b, h, first * tile, std::min((first + take) * tile, len)};
-            plan->segments.insert(plan->segments.end(), seg, seg + 4);
-            plan->item_seg_begin[item + 1] = plan->item_seg_begin[item + 1] + 1;
-            first += take;
-            room -= take;
-        }
-    }
-    plan->cta_seg_begin.push_back(static_cast<int>(plan->segments.size() / 4));
-    for (int i = 0; i < plan->num_items; i++) plan->item_seg_begin[i + 1] += plan->item_seg_begin[i];
-    if (static_cast<int>(plan->cta_seg_begin.size()) != plan->num_ctas + 1) {
-        delete plan;
-        return set_error(PD_INTERNAL, "planner produced an inconsistent CTA table");
-    }
-    *out = plan;
-    return PD_OK;
-}
-
-// Where rows are cut in a few pieces (a long batch: 2-3 segments per row) the decode kernel merges
-// them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
-// the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
-int plan_merge_mode(const pd_plan& pl) {
-    static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
-    const int items = static_cast<int>(pl.item_seg_begin.size()) - 1;
-    if (static_cast<int>(pl.segments.size() / 4) <= items) return 0;
-    int widest = 0;
-    for (int i = 0; i < items; i++) widest = std::max(widest, pl.item_seg_begin[i + 1] - pl.item_seg_begin[i]);
-    return (separate_merge || widest > 4) ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
-}
-
-// The planner's cut with unequal shares: CTA c owns the work units [B_c, B_{c+1}) with
-// B_c = round(total * (w_0 + ... + w_{c-1}) / (w_0 + ... + w_{n-1})).  Same segment rules as build_plan.
-int build_plan_weighted(int tile, const int* seq_lens, int batch, int heads, const std::vector<float>& weights, pd_plan** out) {
-    const int grid = static_cast<int>(weights.size());
-    if (tile <= 0 || batch <= 0 || heads <= 0 || grid <= 0) return set_error(PD_INVALID_ARGUMENT, "weighted plan: bad argument");
-    long long total = 0;
-    for (int b = 0; b < batch; b++) {
-        if (seq_lens[b] <= 0) return set_error(PD_INVALID_ARGUMENT, "make_plan: every sequence needs at least one token");
-        total += static_cast<long long>((seq_lens[b] + tile - 1) / tile) * heads;
-    }
-    double wsum = 0.0;
-    for (float w : weights) wsum += w;
-    std::vector<long long> bound(grid + 1, 0);
-    double acc = 0.0;
-    for (int c = 0; c < grid; c++) {
-        acc += weights[c];
-        bound[c + 1] = std::max(bound[c], std::min<long long>(total, std::llround(total * (acc / wsum))));
-    }
-    bound[grid] = total;
-    pd_plan* plan = new pd_plan();
-    plan->tile = tile;
-    plan->num_items = batch * heads;
-    plan->num_ctas = grid;
-    plan->item_seg_begin.assign(plan->num_items + 1, 0);
-    plan->cta_seg_begin.assign(grid + 1, 0);
-    int cta = 0;
-    long long at = 0;                                           // work units before the current item
-    for (int item = 0; item < plan->num_items; item++) {
-        const int b = item / heads, h = item % heads, len = seq_lens[b];
-        const int tiles = (len + tile - 1) / tile;
-        int first = 0;
-        while (first < tiles) {
-            while (bound[cta + 1] <= at + first) {              // this CTA's share is used up: the next one starts here
-                cta++;
-                plan->cta_seg_begin[cta] = static_cast<int>(plan->segments.size() / 4);
-            }
-            const int take = static_cast<int>(std::min<long long>(bound[cta + 1] - (at + first), tiles - first));
-            const int seg[4] = {b, h, first * tile, std::min((first + take) * tile, len)};
-            plan->segments.insert(plan->segments.end(), seg, seg + 4);
-            plan->item_seg_begin[item + 1]++;
-            first += take;
-        }
-        at += tiles;
-    }
-    for (int c = cta + 1; c <= grid; c++) plan->cta_seg_begin[c] = static_cast<int>(plan->segments.size() / 4);
-    for (int i = 0; i < plan->num_items; i++) plan->item_seg_begin[i + 1] += plan->item_seg_begin[i];
-    *out = plan;
-    return PD_OK;
-}
-
-// Host-side validation of a plan against the lengths it was made for; every index
-// the kernels will dereference is checked here so the device never reads out of range.
-int validate_plan(const pd_plan& plan, const int* seq_lens, int batch, int num_kv_heads) {
-    const int nseg = static_cast<int>(plan.segments.size() / 4);
-    if (static_cast<int>(plan.cta_seg_begin.size()) != plan.num_ctas + 1) return set_error(PD_INTERNAL, "plan: cta table size");
-    for (int c = 0; c < plan.num_ctas; c++)
-        if (plan.cta_seg_begin[c] > plan.cta_seg_begin[c + 1]) return set_error(PD_INTERNAL, "plan: cta table not monotone");
-    if (plan.cta_seg_begin.front() != 0 || plan.cta_seg_begin.back() != nseg) return set_error(PD_INTERNAL, "plan: cta table ends");
-    for (int s = 0; s < nseg; s++) {
-        const int* g = &plan.segments[4 * s];
-        if (g[0] < 0 || g[0] >= batch || g[1] < 0 || g[1] >= num_kv_heads || g[2] < 0 || g[2] >= g[3] ||
-            g[3] > seq_lens[g[0]] || g[2] % plan.tile != 0)
-            return set_error(PD_INTERNAL, "plan: segment %d out of range", s);
-    }
-    return PD_OK;
-}
-
-}  // namespace
+#include "host_plan.hpp"
 
 // ---- DevicePlan ---------------------------------------------------------------------------------
 
@@ -861,6 +598,21 @@ void pd_device_plan_destroy(pd_device_plan* dp) {
     delete dp;
 }
 
+}  // extern "C"
+namespace {
+// One wave of the head-fused kernel: SMs x CTAs per SM (one, by shared memory).
+int fused_wave(const KernelInfo* fk) {
+    int dev = 0, sms = 0, resident = 0;
+    if (fk && configure(fk) == PD_OK && cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fk->fn, fk->threads, fk->smem) == cudaSuccess)
+        return sms * std::min(resident, fk->per_sm);
+    cudaGetLastError();
+    return 0;
+}
+}  // namespace
+extern "C" {
+
 int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, int head_dim, void* stream_) {
     if (!dp || !plan) return set_error(PD_INVALID_ARGUMENT, "device_plan_upload: null argument");
     if (group <= 0 || head_dim <= 0) return set_error(PD_INVALID_ARGUMENT, "device_plan_upload: group and head_dim must be positive");
@@ -877,13 +629,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         (plan->num_q_heads == 0 || plan->num_q_heads / plan->num_kv_heads == group) && head_dim == 128) {
         fk = fused_info<__half>(group);
         int grid = plan->forced_ctas;
-        if (fk && grid <= 0) {
-            int dev = 0, sms = 0, resident = 0;
-            if (configure(fk) == PD_OK && cudaGetDevice(&dev) == cudaSuccess &&
-                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fk->fn, fk->threads, fk->smem) == cudaSuccess)
-                grid = sms * std::min(resident, fk->per_sm);
-        }
+        if (fk && grid <= 0) grid = fused_wave(fk);
         if (!fk || grid <= 0 ||
             build_plan(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
             rows_plan = nullptr;
@@ -1069,7 +815,22 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     const size_t item_bytes = round16(sizeof(int) * (items + 1));
     const size_t row_bytes  = round16(sizeof(int) * (batch + 1));
     const size_t info_bytes = round16(sizeof(int) * pdk::PLAN_INFO_INTS);
-    const size_t total = seg_bytes + cta_bytes + item_bytes + row_bytes + info_bytes;
+    // The head-fused schedule of the same step, where the layer allows it and the batch is wide enough for
+    // rows to be cut in few pieces (how they are really cut is only known on the device: each row decides
+    // by its own piece count who merges it, see MERGE_HYBRID).
+    const KernelInfo* fk = nullptr;
+    int fgrid = 0;
+    if (dtype == PD_FP16 && num_kv_heads == FUSED_HEADS && head_dim == 128 && g_head_fused != 0) {
+        fk = fused_info<__half>(group);
+        fgrid = num_ctas > 0 ? num_ctas : fused_wave(fk);
+        if (!fk || fgrid <= 0 || (g_head_fused == 1 && batch * 3 < fgrid)) { fk = nullptr; fgrid = 0; }
+    }
+    const size_t fcap_seg   = fk ? static_cast<size_t>(batch) + fgrid : 0;
+    const size_t fseg_bytes = fk ? round16(sizeof(int4) * fcap_seg) : 0;
+    const size_t fcta_bytes = fk ? round16(sizeof(int) * (fgrid + 1)) : 0;
+    const size_t frow_bytes = fk ? round16(sizeof(int) * (batch + 1)) : 0;
+    const size_t std_bytes  = seg_bytes + cta_bytes + item_bytes + row_bytes + info_bytes;
+    const size_t total = std_bytes + fseg_bytes + fcta_bytes + 2 * frow_bytes + (fk ? info_bytes : 0);
     const void* old_key = dp->segments;
     if (total > dp->arena_cap) {
         PD_CUDA(cudaFree(dp->arena));
@@ -1078,7 +839,9 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         dp->arena_cap = total;
     }
     const size_t rows = cap_seg * group;
-    const size_t need = rows * (head_dim + 1) + items;
+    const size_t std_need = rows * (head_dim + 1) + items;
+    const size_t frows = fcap_seg * num_q_heads;
+    const size_t need = std_need + (fk ? frows * (head_dim + 1) + items : 0);
     if (need > dp->partial_cap) {
         PD_CUDA(cudaFree(dp->partial));
         dp->partial = nullptr; dp->partial_cap = 0;
@@ -1102,14 +865,10 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     dp->fused           = pd_device_plan::Fused{};
     dp->weighted        = pd_device_plan::Fused{};
     dp->stats           = nullptr;
-    {
-        std::lock_guard<std::mutex> lock(g_fused_mutex);
-        if (old_key) g_fused_registry.erase(old_key);
-        g_fused_registry.erase(dp->segments);
-    }
     pdk::PlanJob job{};
     job.seq_lens = d_seq_lens; job.slot_ids = d_slot_ids;
-    job.batch = batch; job.num_kv_heads = num_kv_heads; job.group = group; job.tile = k->tile; job.grid = grid;
+    job.batch = batch; job.num_kv_heads = num_kv_heads; job.tile = k->tile; job.grid = grid;
+    job.lse_per_segment = group; job.num_counters = static_cast<int>(items);
     job.segments = reinterpret_cast<int4*>(a);
     job.cta_seg_begin = const_cast<int*>(dp->cta_seg_begin);
     job.item_seg_begin = const_cast<int*>(dp->item_seg_begin);
@@ -1118,6 +877,38 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     job.partial_lse = dp->partial_lse;
     pdk::plan_kernel<<<1, pdk::PLAN_THREADS, 0, stream>>>(job);
     PD_CUDA(cudaGetLastError());
+    if (fk) {
+        char* fa = a + std_bytes;
+        auto& f = dp->fused;
+        f.valid = true;
+        f.dtype = dtype; f.group = group; f.batch = batch;
+        f.num_ctas = fgrid;
+        f.num_segments = static_cast<int>(fcap_seg);
+        f.needs_merge = pdk::MERGE_HYBRID;
+        f.rows = frows;
+        f.segments = fa;
+        f.cta_seg_begin = reinterpret_cast<const int*>(fa + fseg_bytes);
+        f.row_seg_begin = reinterpret_cast<const int*>(fa + fseg_bytes + fcta_bytes);
+        f.partial_out = dp->partial + std_need;
+        pdk::PlanJob fj{};
+        fj.seq_lens = d_seq_lens; fj.slot_ids = d_slot_ids;
+        fj.batch = batch; fj.num_kv_heads = 1; fj.tile = FUSED_TILE; fj.grid = fgrid;   // work items are rows
+        fj.lse_per_segment = num_q_heads; fj.num_counters = static_cast<int>(items);
+        fj.segments = reinterpret_cast<int4*>(fa);
+        fj.cta_seg_begin = const_cast<int*>(f.cta_seg_begin);
+        fj.item_seg_begin = const_cast<int*>(f.row_seg_begin);
+        fj.row_tile_begin = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + frow_bytes);
+        fj.info = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + 2 * frow_bytes);
+        fj.partial_lse = f.partial_out + frows * head_dim;
+        pdk::plan_kernel<<<1, pdk::PLAN_THREADS, 0, stream>>>(fj);
+        PD_CUDA(cudaGetLastError());
+    }
+    {
+        std::lock_guard<std::mutex> lock(g_fused_mutex);
+        if (old_key) g_fused_registry.erase(old_key);
+        if (dp->fused.valid) g_fused_registry[dp->segments] = AltSchedules{dp->fused, dp->weighted, nullptr};
+        else g_fused_registry.erase(dp->segments);
+    }
     return PD_OK;
 }
 

@@ -27,7 +27,9 @@ constexpr int PLAN_INFO_INTS     = 4;
 struct PlanJob {
     const int* seq_lens;       // [slots], device
     const int* slot_ids;       // [batch] or null = identity
-    int batch, num_kv_heads, group, tile, grid;
+    int batch, num_kv_heads, tile, grid;
+    int lse_per_segment;       // LSE slots per segment: the GQA group, or all query heads for head-fused row plans
+    int num_counters;          // arrival counters to clear: one per (row, kv head) of the layer
     int4* segments;            // capacity batch * num_kv_heads + grid
     int*  cta_seg_begin;       // [grid + 1]
     int*  item_seg_begin;      // [batch * num_kv_heads + 1]
@@ -130,8 +132,8 @@ plan_kernel(const PlanJob j)
         }
     }
     for (int c = ctas + tid; c <= j.grid; c += PLAN_THREADS) j.cta_seg_begin[c] = nseg;   // idle CTAs: empty ranges
-    int* counters = reinterpret_cast<int*>(j.partial_lse + static_cast<size_t>(nseg) * j.group);
-    for (int i = tid; i < items; i += PLAN_THREADS) counters[i] = 0;
+    int* counters = reinterpret_cast<int*>(j.partial_lse + static_cast<size_t>(nseg) * j.lse_per_segment);
+    for (int i = tid; i < j.num_counters; i += PLAN_THREADS) counters[i] = 0;
     __syncthreads();
     if (tid == 0) {
         j.info[PLAN_INFO_CTAS] = ctas;

@@ -81,7 +81,7 @@ def test_decode_with_device_plan_gives_the_host_plan_bits(dtype, lens, ctas, tor
     cache, model, cfg = build_cache(case, K, V, torch, pa)
     q = torch.randn(len(lens), 32, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(2)).cuda()
     before = pa.head_fused()
-    pa.set_head_fused(0)          # the device planner always schedules by (row, kv head)
+    pa.set_head_fused(0)          # batches this narrow get no head-fused variant from the device planner
     try:
         host_plan = pa.make_plan(pa.KVDtype(dtype), lens, 32, 8, 128, ctas)
         hp = pa.DevicePlan()
@@ -201,4 +201,33 @@ def test_plan_and_decode_replay_in_a_cuda_graph(torch_cuda, pa):
             assert torch.equal(out, want), f"step {step}"
     finally:
         pa.set_head_fused(before)
+    cache.close()
+
+
+@pytest.mark.parametrize("lens,ctas", [([700] * 60 + [3000, 64, 1], 0), ([20000, 5000] + [300] * 58, 0), ([513] * 9, 5)])
+def test_device_plan_runs_the_head_fused_schedule_too(lens, ctas, torch_cuda, pa):
+    """fp16, 8 kv heads, a wide batch: the device planner also cuts the step by rows for the head-fused
+    kernel.  Its result has the bits of the host-planned head-fused step: same cut, and rows cut in more
+    than 4 pieces are merged by the same separate kernel in both."""
+    torch = torch_cuda
+    case = Case(FP16, 32, 8, 16, lens, shuffle=2, seed=41)
+    K, V = seeded_kv(case.seq_lens, case.hkv, case.d, case.seed)
+    cache, model, cfg = build_cache(case, K, V, torch, pa)
+    q = torch.randn(len(lens), 32, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(6)).cuda()
+    before = pa.head_fused()
+    pa.set_head_fused(2)
+    try:
+        hp = pa.DevicePlan()
+        hp.upload(pa.make_plan(pa.KVDtype.FP16, lens, 32, 8, 128, ctas), 4, 128)
+        want = _decode_with(torch, pa, FP16, cache, cfg, q, lens, hp)
+        dp = pa.DevicePlan()
+        dp.build(FP16, torch.tensor(lens, dtype=torch.int32, device="cuda"), len(lens), 32, 8, 128, ctas)
+        got = _decode_with(torch, pa, FP16, cache, cfg, q, lens, dp)
+        pa.set_head_fused(0)
+        plain = _decode_with(torch, pa, FP16, cache, cfg, q, lens, dp)
+    finally:
+        pa.set_head_fused(before)
+    assert torch.equal(got, want)
+    assert not torch.equal(got, plain), "mode 0 runs the (row, kv head) schedule of the same device plan"
+    assert (got.float() - plain.float()).abs().max().item() <= TOL
     cache.close()
