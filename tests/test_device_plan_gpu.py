@@ -81,22 +81,22 @@ def test_decode_with_device_plan_gives_the_host_plan_bits(dtype, lens, ctas, tor
     cache, model, cfg = build_cache(case, K, V, torch, pa)
     q = torch.randn(len(lens), 32, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(2)).cuda()
     before = pa.head_fused()
-    pa.set_head_fused(0)          # batches this narrow get no head-fused variant from the device planner
+    pa.set_head_fused(0)          # the (row, kv head) schedule on both sides; the head-fused one has its own test
     try:
         host_plan = pa.make_plan(pa.KVDtype(dtype), lens, 32, 8, 128, ctas)
         hp = pa.DevicePlan()
         hp.upload(host_plan, 4, 128)
         want = _decode_with(torch, pa, dtype, cache, cfg, q, lens, hp)
+        dp = pa.DevicePlan()
+        dp.build(dtype, torch.tensor(lens, dtype=torch.int32, device="cuda"), len(lens), 32, 8, 128, ctas)
+        got = _decode_with(torch, pa, dtype, cache, cfg, q, lens, dp)
+        assert torch.isfinite(got).all()
+        assert torch.equal(got, want)
+        # a second step with the same device plan object (counters re-armed, buffers reused)
+        dp.build(dtype, torch.tensor(lens, dtype=torch.int32, device="cuda"), len(lens), 32, 8, 128, ctas)
+        assert torch.equal(_decode_with(torch, pa, dtype, cache, cfg, q, lens, dp), want)
     finally:
         pa.set_head_fused(before)
-    dp = pa.DevicePlan()
-    dp.build(dtype, torch.tensor(lens, dtype=torch.int32, device="cuda"), len(lens), 32, 8, 128, ctas)
-    got = _decode_with(torch, pa, dtype, cache, cfg, q, lens, dp)
-    assert torch.isfinite(got).all()
-    assert torch.equal(got, want)
-    # a second step with the same device plan object (counters re-armed, buffers reused)
-    dp.build(dtype, torch.tensor(lens, dtype=torch.int32, device="cuda"), len(lens), 32, 8, 128, ctas)
-    assert torch.equal(_decode_with(torch, pa, dtype, cache, cfg, q, lens, dp), want)
     cache.close()
 
 
