@@ -719,11 +719,13 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // [segments][heads] LSEs, then one arrival counter per (row, kv head) for the in-kernel merge (zero
     // between launches: the merging warp re-arms its counter).
     const size_t rows = nseg * group;
-    const size_t std_need = rows * (head_dim + 1) + plan->num_items;
+    // every region starts on a 16-byte boundary: the merges read partial rows as float4
+    auto round4 = [](size_t floats) { return (floats + 3) & ~static_cast<size_t>(3); };
+    const size_t std_need = round4(rows * (head_dim + 1) + plan->num_items);
     const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * static_cast<size_t>(group) * FUSED_HEADS : 0;
-    const size_t f_need = rows_plan ? frows * (head_dim + 1) + plan->num_items : 0;
+    const size_t f_need = rows_plan ? round4(frows * (head_dim + 1) + plan->num_items) : 0;
     const size_t wrows = weighted_plan ? (weighted_plan->segments.size() / 4) * static_cast<size_t>(group) : 0;
-    const size_t w_need = weighted_plan ? wrows * (head_dim + 1) + plan->num_items : 0;
+    const size_t w_need = weighted_plan ? round4(wrows * (head_dim + 1) + plan->num_items) : 0;
     const size_t need = std_need + f_need + w_need;
     if (need > dp->partial_cap) {
         PD_CUDA(cudaFree(dp->partial));
@@ -839,7 +841,7 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         dp->arena_cap = total;
     }
     const size_t rows = cap_seg * group;
-    const size_t std_need = rows * (head_dim + 1) + items;
+    const size_t std_need = (rows * (head_dim + 1) + items + 3) & ~static_cast<size_t>(3);   // float4 reads of the next region
     const size_t frows = fcap_seg * num_q_heads;
     const size_t need = std_need + (fk ? frows * (head_dim + 1) + items : 0);
     if (need > dp->partial_cap) {

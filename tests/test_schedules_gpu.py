@@ -167,3 +167,16 @@ def test_plan_rebuilt_from_arrays_gets_both_schedules(torch_cuda, pa):
     assert not torch.equal(outs["rebuilt", 2], outs["rebuilt", 0]), "the two schedules round differently somewhere"
     assert (outs["rebuilt", 2].float() - outs["rebuilt", 0].float()).abs().max().item() <= TOL
     cache.close()
+
+
+@pytest.mark.parametrize("hq", [8, 16])
+@pytest.mark.parametrize("ctas", [0, 37, 50, 99])
+def test_small_groups_with_split_rows(hq, ctas, torch_cuda, pa, both_schedules):
+    """Groups of 1 and 2 query heads per kv head with rows cut across CTAs: the second schedule's partial
+    rows start wherever the first schedule's workspace ends, and the merges read them 16 bytes at a time,
+    so every region of the workspace has to start on a 16-byte boundary for any segment count."""
+    case = Case(FP16, hq, 8, 16, [3000] * 21 + [17], num_ctas=ctas, shuffle=4, seed=15)
+    (e1, o1, _, i1), (e2, o2, _, _) = both_schedules(lambda: run_case(case, torch_cuda, pa))
+    assert e1 <= TOL and e2 <= TOL, (e1, e2)
+    assert float(np.abs(o1 - o2).max()) <= TOL
+    assert i1["segments"] > 22 * 8, "rows are split"
