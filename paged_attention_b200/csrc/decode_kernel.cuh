@@ -24,6 +24,13 @@
 //    (fp16) and 16-byte loads (fp8) are conflict-free for page sizes >= 8.
 //  * Every wait is bounded; on expiry the CTA records a code in a status word,
 //    raises a CTA-wide abort flag and drains its copies.  Nothing traps.
+//  * A second tile shape (Config::HEADS = 8) takes 16 tokens of all 8 kv heads per tile, one consumer
+//    warp per kv head, with rows (not (row, kv head) pairs) as the plan's work items: a page's K (or V)
+//    block is then one contiguous 32 KB copy.
+//  * Rows cut in a few pieces are merged by the decode kernel itself (the last piece to arrive does it);
+//    the merge kernel, launched as a programmatic dependent, handles rows cut in many pieces.
+//  * Optional extras behind null pointers: per-kv-head scales, outputs stored into the gathered buffers
+//    of peer GPUs, a per-CTA record of busy time and tiles for the host's adaptive cut.
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -38,7 +45,6 @@ namespace pdk {
 constexpr int HEAD_DIM = 128;
 constexpr int OSTRIDE  = HEAD_DIM + 4;   // padded row of the cross-warp merge scratch (floats)
 
-// status word codes (code << 24 | blockIdx)
 // diagnostic flags carried above the box-size bits of the kernel's btl_flags argument
 constexpr int FLAG_LOAD_ONLY = 0x100;
 constexpr int FLAG_NO_L2_HINT = 0x200;
@@ -54,6 +60,7 @@ constexpr int MERGE_IN_KERNEL = 2;
 constexpr int MERGE_HYBRID = 3;
 constexpr int HYBRID_MAX_PIECES = 4;
 
+// status word codes (code << 24 | blockIdx)
 constexpr unsigned ST_FULL_TIMEOUT  = 1;   // consumer gave up waiting for a tile
 constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a free stage
 constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
