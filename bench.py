@@ -382,8 +382,11 @@ def our_arm(args, wl):
         torch.cuda.synchronize()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    warmup = max(args.warmup, 24)   # the adaptive cut settles within about 20 plans
-    for _ in range(warmup):
+    # W warm-up steps as asked (at least 3), preceded by as many settling steps as it takes to make 24 in
+    # all: the adaptive cut needs about 20 plans to settle, as it would have in any serving loop
+    warmup = max(args.warmup, 3)
+    settle = max(0, 24 - warmup)
+    for _ in range(settle + warmup):
         replan()
         flush()
         step()
@@ -436,7 +439,8 @@ def our_arm(args, wl):
                        "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
                        "ctas": plan.num_ctas, "segments": plan.num_segments, "tile": plan.tile,
                        "kernel_variant": pa.kernel_variant(),
-                       "plan": "uploaded before every warm-up step, timed steps reuse the last one; adaptive cut %s" % ("on" if pa.adaptive_cut() else "off"),
+                       "plan": "uploaded before every warm-up step, timed steps reuse the last one; adaptive cut %s; %d settling steps before the warm-up"
+                               % ("on" if pa.adaptive_cut() else "off", settle),
                        "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
                              % (local_bytes / 1e6),
                        "timing": "CUDA events around decode+merge%s per step, summed over steps, max over ranks"
