@@ -148,10 +148,10 @@ def test_plan_rebuilt_from_arrays_gets_both_schedules(torch_cuda, pa):
     outs = {}
     try:
         for name, plan in (("made", made), ("rebuilt", rebuilt)):
-            dp = pa.DevicePlan()
-            dp.upload(plan, 4, 128)
             for mode in (2, 0):
-                pa.set_head_fused(mode)
+                pa.set_head_fused(mode)          # before the upload: it decides which schedules the device plan carries
+                dp = pa.DevicePlan()
+                dp.upload(plan, 4, 128)
                 p = cache.params()
                 out = torch.zeros_like(q)
                 p.q, p.out, p.batch, p.num_q_heads = q.data_ptr(), out.data_ptr(), len(lens), 32
