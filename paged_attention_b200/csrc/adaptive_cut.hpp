@@ -103,6 +103,11 @@ void update_weights(RateTable* t, cudaStream_t stream) {
     // microseconds of ramp-up and epilogue do not matter, say something about streaming rates.
     if (valid < n || busy_total / static_cast<double>(launches) / n < 120000.0) return;
     const double mean = sum / valid;
+    // SMs of one GPU differ by 10 % or so; a reading that spreads over more than 1.5x saw something else
+    // (another stream's kernels sharing the SMs, a preempted context) and says nothing about the SMs.
+    double lo = rate[0], hi = rate[0];
+    for (int c = 1; c < n; c++) { lo = std::min(lo, rate[c]); hi = std::max(hi, rate[c]); }
+    if (hi > 1.5 * lo) return;
     if (t->weights.empty()) t->weights.assign(n, 1.0f);
     const double gain = t->updates < 4 ? 0.5 : 0.3;
     double wsum = 0.0;
