@@ -130,6 +130,10 @@ int pd_head_fused(void);
 int pd_set_adaptive_cut(int on);
 int pd_adaptive_cut(void);
 int pd_adaptive_cut_reset(void);
+/* Folds the latest per-CTA readings of the current device into the weights (what pd_device_plan_upload
+ * and pd_device_plan_build do on their own); for callers that replay a CUDA graph holding a device-side
+ * plan and therefore never come through those calls.  Does not wait for the device. */
+int pd_adaptive_cut_refresh(void* stream);
 /* Introspection: the index-th rate table (no particular order).  Returns its grid size (0: no such table)
  * and fills, up to cap CTAs, weights[c] (relative share of CTA c, mean 1) and record[2c], record[2c+1] (total
  * busy nanoseconds and tiles of CTA c at the last reading), record[2 * grid] launches; either may be NULL,
@@ -189,8 +193,12 @@ int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
  * kernel, the others by the merge kernel, which is always launched (the host cannot know).  For fp16
  * layers with 8 kv heads and at least a third as many rows as the one-CTA-per-SM grid has CTAs, a second
  * launch of the same planner also cuts the step by rows for the head-fused schedule (pd_set_head_fused).
- * The adaptive cut does not apply to plans cut on the device.  A length <= 0 gives that row no work and
- * is reported by pd_device_plan_info (the host planner refuses such a batch).
+ * With the adaptive cut on, the planner reads the per-CTA shares the host has derived so far from a
+ * device array with a stable address (grids up to 1024 CTAs, steps with at least 8 work units per CTA;
+ * otherwise the equal cut) and produces the cut of pd_make_plan_weighted for them; the call folds new
+ * readings in unless the stream is being captured, and a caller that replays a captured step calls
+ * pd_adaptive_cut_refresh between replays.  A length <= 0 gives that row no work and is reported by
+ * pd_device_plan_info (the host planner refuses such a batch).
  * pd_device_plan_info (waits for the stream): out[0] CTAs with work, out[1] segments, out[2] most pieces
  * any (row, kv head) was cut in, out[3] 1 + first row with a length <= 0 (0: none).
  * pd_device_plan_fetch (waits for the stream): the plan as a host object, for inspection and tests. */

@@ -66,6 +66,7 @@ SIGNATURES = {
     "pd_set_adaptive_cut": (C.c_int, [C.c_int]),
     "pd_adaptive_cut": (C.c_int, []),
     "pd_adaptive_cut_reset": (C.c_int, []),
+    "pd_adaptive_cut_refresh": (C.c_int, [_vp]),
     "pd_adaptive_cut_table": (C.c_int, [C.c_int, _vp, _vp, C.c_int]),
     "pd_set_head_fused": (C.c_int, [C.c_int]),
     "pd_head_fused": (C.c_int, []),

@@ -21,6 +21,10 @@ struct RateTable {
     bool copy_queued = false;
     std::vector<float> weights;              // mean 1; empty until the first usable record
     int updates = 0;
+    // For the device-side planner: shares[0] = 1.0 once weights exist (0.0: cut in equal shares), then
+    // shares[1 + c] = (w_0 + .. + w_c-1) / sum(w) for c = 0..grid.  Device memory with a stable address, so a
+    // captured plan kernel picks up whatever the host wrote last.
+    double* shares = nullptr;
 };
 struct RateKey {
     int device; const void* fn; int grid;
@@ -42,13 +46,17 @@ RateTable* rate_table(const void* fn, int grid) {
     RateTable& t = g_rates[RateKey{dev, fn, grid}];
     if (!t.slots) {
         const size_t bytes = sizeof(unsigned long long) * (2 * grid + 1);   // + launches so far
+        const size_t share_bytes = sizeof(double) * (grid + 2);
         void* dev_mem = nullptr;
         void* host = nullptr;
+        void* share_mem = nullptr;
         if (cudaMalloc(&dev_mem, bytes) != cudaSuccess || cudaMemset(dev_mem, 0, bytes) != cudaSuccess ||
+            cudaMalloc(&share_mem, share_bytes) != cudaSuccess || cudaMemset(share_mem, 0, share_bytes) != cudaSuccess ||
             cudaMallocHost(&host, bytes) != cudaSuccess ||
             cudaEventCreateWithFlags(&t.copied, cudaEventDisableTiming) != cudaSuccess) {
             cudaGetLastError();
             cudaFree(dev_mem);
+            cudaFree(share_mem);
             cudaFreeHost(host);
             g_rates.erase(RateKey{dev, fn, grid});
             return nullptr;
@@ -56,6 +64,7 @@ RateTable* rate_table(const void* fn, int grid) {
         std::memset(host, 0, bytes);
         t.slots = static_cast<unsigned long long*>(dev_mem);
         t.host = static_cast<unsigned long long*>(host);
+        t.shares = static_cast<double*>(share_mem);
         t.seen.assign(2 * static_cast<size_t>(grid) + 1, 0);
         t.grid = grid;
     }
@@ -101,23 +110,37 @@ void update_weights(RateTable* t, cudaStream_t stream) {
     t->seen.assign(t->host, t->host + 2 * static_cast<size_t>(n) + 1);
     // Only launches in which every CTA worked, and for long enough (120 us on average) that its few
     // microseconds of ramp-up and epilogue do not matter, say something about streaming rates.
-    if (valid < n || busy_total / static_cast<double>(launches) / n < 120000.0) return;
+    // (The equal cut can leave the last CTA or two of a grid without work; they keep their weight.)
+    if (valid < n - std::max(2, n / 64) || busy_total / static_cast<double>(launches) / valid < 120000.0) return;
     const double mean = sum / valid;
     // SMs of one GPU differ by 10 % or so; a reading that spreads over more than 1.5x saw something else
     // (another stream's kernels sharing the SMs, a preempted context) and says nothing about the SMs.
-    double lo = rate[0], hi = rate[0];
-    for (int c = 1; c < n; c++) { lo = std::min(lo, rate[c]); hi = std::max(hi, rate[c]); }
+    double lo = mean, hi = mean;
+    for (int c = 0; c < n; c++)
+        if (rate[c] > 0.0) { lo = std::min(lo, rate[c]); hi = std::max(hi, rate[c]); }
     if (hi > 1.5 * lo) return;
     if (t->weights.empty()) t->weights.assign(n, 1.0f);
     const double gain = t->updates < 4 ? 0.5 : 0.3;
     double wsum = 0.0;
     for (int c = 0; c < n; c++) {
+        if (!(rate[c] > 0.0)) { wsum += t->weights[c]; continue; }
         const double target = std::min(1.3, std::max(0.7, rate[c] / mean));
         t->weights[c] = static_cast<float>((1.0 - gain) * t->weights[c] + gain * target);
         wsum += t->weights[c];
     }
     for (int c = 0; c < n; c++) t->weights[c] = static_cast<float>(t->weights[c] * n / wsum);
     t->updates++;
+    // the same cumulative shares build_plan_weighted computes, for the device-side planner
+    std::vector<double> shares(n + 2, 0.0);
+    double total = 0.0, acc = 0.0;
+    for (float w : t->weights) total += w;
+    shares[0] = 1.0;
+    for (int c = 0; c < n; c++) {
+        acc += t->weights[c];
+        shares[2 + c] = acc / total;
+    }
+    if (cudaMemcpyAsync(t->shares, shares.data(), sizeof(double) * (n + 2), cudaMemcpyHostToDevice, stream) != cudaSuccess)
+        cudaGetLastError();   // pageable source: the call returns once the bytes are staged
 }
 
 }  // namespace

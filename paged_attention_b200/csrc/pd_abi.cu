@@ -96,7 +96,7 @@ void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap&
 template<typename Kernel>
 void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_t stream) {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.gridDim = dim3(static_cast<unsigned>(std::min(blocks, 148 * 8)));   // the kernel walks its pairs
     cfg.blockDim = dim3(128);
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -417,11 +417,25 @@ int pd_adaptive_cut_table(int index, float* weights, unsigned long long* record,
     }
     return 0;
 }
+int pd_adaptive_cut_refresh(void* stream_) {
+    int dev = 0;
+    PD_CUDA(cudaGetDevice(&dev));
+    std::vector<RateTable*> tables;
+    {
+        std::lock_guard<std::mutex> lock(g_rate_mutex);
+        for (auto& kv : g_rates)
+            if (kv.first.device == dev) tables.push_back(&kv.second);
+    }
+    if (g_adaptive)
+        for (RateTable* t : tables) update_weights(t, static_cast<cudaStream_t>(stream_));
+    return PD_OK;
+}
 int pd_adaptive_cut_reset(void) {
     std::lock_guard<std::mutex> lock(g_rate_mutex);
     for (auto& kv : g_rates) {
         kv.second.weights.clear();
         kv.second.updates = 0;
+        if (kv.second.shares) cudaMemset(kv.second.shares, 0, sizeof(double));   // device plans go back to equal shares
         if (kv.second.copy_queued) cudaEventSynchronize(kv.second.copied);
         kv.second.copy_queued = false;
         if (kv.second.host) kv.second.seen.assign(kv.second.host, kv.second.host + 2 * static_cast<size_t>(kv.second.grid) + 1);
@@ -877,6 +891,20 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     job.row_tile_begin = dp->row_tile_begin;
     job.info = dp->info;
     job.partial_lse = dp->partial_lse;
+    // Adaptive cut: the planner reads the shares the host derived from earlier launches (device memory
+    // with a stable address, so a captured plan keeps following them), and the decode launches of this plan
+    // add to the same record.  The host folds new readings in here unless the stream is being captured;
+    // callers that replay a captured step call pd_adaptive_cut_refresh between replays instead.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) { cudaGetLastError(); capture = cudaStreamCaptureStatusActive; }
+    const bool capturing = capture != cudaStreamCaptureStatusNone;
+    if (g_adaptive && batch > 0) {
+        if (RateTable* t = rate_table(k->fn, grid)) {
+            if (!capturing) update_weights(t, stream);
+            job.shares = t->shares;
+            dp->stats = t->slots;
+        }
+    }
     pdk::plan_kernel<<<1, pdk::PLAN_THREADS, 0, stream>>>(job);
     PD_CUDA(cudaGetLastError());
     if (fk) {
@@ -902,13 +930,20 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         fj.row_tile_begin = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + frow_bytes);
         fj.info = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + 2 * frow_bytes);
         fj.partial_lse = f.partial_out + frows * head_dim;
+        if (g_adaptive && batch > 0) {
+            if (RateTable* t = rate_table(fk->fn, fgrid)) {
+                if (!capturing) update_weights(t, stream);
+                fj.shares = t->shares;
+                f.stats = t->slots;
+            }
+        }
         pdk::plan_kernel<<<1, pdk::PLAN_THREADS, 0, stream>>>(fj);
         PD_CUDA(cudaGetLastError());
     }
     {
         std::lock_guard<std::mutex> lock(g_fused_mutex);
         if (old_key) g_fused_registry.erase(old_key);
-        if (dp->fused.valid) g_fused_registry[dp->segments] = AltSchedules{dp->fused, dp->weighted, nullptr};
+        if (dp->fused.valid || dp->stats) g_fused_registry[dp->segments] = AltSchedules{dp->fused, dp->weighted, dp->stats};
         else g_fused_registry.erase(dp->segments);
     }
     return PD_OK;

@@ -9,6 +9,11 @@
 // [P_i, P_i + tiles_i), so it is cut at every multiple of `per` strictly inside that range, and the
 // piece that starts at c * per is the first segment of CTA c.  Two block-wide prefix sums (tiles per
 // row, pieces per item) are all the communication the cut needs; one CTA of 1024 threads does it.
+//
+// With cumulative shares from the host's adaptive cut (PlanJob::shares, active once the host has seen
+// usable rates) the cut points become B_c = round(total * share_c) instead of c * per: the cut of the host's
+// weighted planner, bit for bit.  Only for grids up to PLAN_MAX_WEIGHTED CTAs and at least 8 units per CTA,
+// so that no CTA's share is empty; otherwise the equal cut stands.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -16,6 +21,7 @@
 namespace pdk {
 
 constexpr int PLAN_THREADS = 1024;
+constexpr int PLAN_MAX_WEIGHTED = 1024;
 
 // Slots of the `info` array the planner leaves behind for the host (diagnostics, tests).
 constexpr int PLAN_INFO_CTAS     = 0;   // CTAs that received work (the rest of the grid idles)
@@ -36,6 +42,7 @@ struct PlanJob {
     int*  row_tile_begin;      // [batch + 1] scratch: tiles of one kv head before each row
     int*  info;                // [PLAN_INFO_INTS]
     float* partial_lse;        // the arrival counters of the in-kernel merge follow segments * group LSEs
+    const double* shares;      // null, or [0] = active flag, [1 + c] = cumulative share before CTA c, c = 0..grid
 };
 
 // Exclusive prefix sum of value(0..n-1) into out[0..n] (out[n] = total), all threads of the block.
@@ -83,6 +90,7 @@ plan_kernel(const PlanJob j)
     __shared__ int warp_sums[32];
     __shared__ int carry;
     __shared__ int widest, bad_row;
+    __shared__ int bound[PLAN_MAX_WEIGHTED + 1];   // weighted cut: first unit of every CTA
     const int tid = threadIdx.x;
     if (tid == 0) { widest = 0; bad_row = 0; }
     __syncthreads();
@@ -97,7 +105,26 @@ plan_kernel(const PlanJob j)
     const long long total = static_cast<long long>(row_total) * j.num_kv_heads;
     const int items = j.batch * j.num_kv_heads;
     const long long per = total > 0 ? (total + j.grid - 1) / j.grid : 1;
-    const int ctas = total > 0 ? static_cast<int>((total + per - 1) / per) : 0;
+    const bool weighted = j.shares != nullptr && j.grid <= PLAN_MAX_WEIGHTED && total >= 8LL * j.grid &&
+                          total < (1LL << 31) && j.shares[0] != 0.0;
+    const int ctas = total > 0 ? (weighted ? j.grid : static_cast<int>((total + per - 1) / per)) : 0;
+    if (weighted) {
+        for (int c = tid; c <= j.grid; c += PLAN_THREADS) {
+            long long b = llround(static_cast<double>(total) * j.shares[1 + c]);
+            if (b > total) b = total;
+            bound[c] = static_cast<int>(c == j.grid ? total : b);
+        }
+        __syncthreads();
+    }
+    // weighted cut: the CTA that owns unit t, i.e. the largest c with bound[c] <= t
+    auto cta_of = [&](long long t) {
+        int lo = 0, hi = j.grid - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (bound[mid] <= t) lo = mid; else hi = mid - 1;
+        }
+        return lo;
+    };
 
     // units before item i, and its own
     auto item_begin = [&](int i) {
@@ -110,7 +137,8 @@ plan_kernel(const PlanJob j)
         const int t = j.row_tile_begin[b + 1] - j.row_tile_begin[b];
         if (t == 0) return 0;
         const long long p0 = item_begin(i);
-        const int n = static_cast<int>((p0 + t - 1) / per - p0 / per) + 1;
+        const int n = weighted ? cta_of(p0 + t - 1) - cta_of(p0) + 1
+                               : static_cast<int>((p0 + t - 1) / per - p0 / per) + 1;
         atomicMax(&widest, n);
         return n;
     };
@@ -123,6 +151,16 @@ plan_kernel(const PlanJob j)
         const int len = row_len(b);
         const long long p0 = item_begin(i), p1 = p0 + t;
         int idx = j.item_seg_begin[i];
+        if (weighted) {
+            for (int c = cta_of(p0); c < j.grid && bound[c] < p1; c++, idx++) {
+                const long long from = bound[c] > p0 ? bound[c] : p0;
+                const long long to   = bound[c + 1] < p1 ? bound[c + 1] : p1;
+                const int tok_end = static_cast<int>(to - p0) * j.tile;
+                j.segments[idx] = make_int4(b, h, static_cast<int>(from - p0) * j.tile, tok_end < len ? tok_end : len);
+                if (from == bound[c]) j.cta_seg_begin[c] = idx;
+            }
+            continue;
+        }
         for (long long c = p0 / per; c * per < p1; c++, idx++) {
             const long long from = c * per > p0 ? c * per : p0;
             const long long to   = (c + 1) * per < p1 ? (c + 1) * per : p1;

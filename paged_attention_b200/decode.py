@@ -94,6 +94,11 @@ def adaptive_cut_reset():
     check(_lib.lib().pd_adaptive_cut_reset())
 
 
+def adaptive_cut_refresh(stream=0):
+    """Fold the latest per-CTA readings into the weights; for loops that replay a captured device-side plan."""
+    check(_lib.lib().pd_adaptive_cut_refresh(stream))
+
+
 def adaptive_cut_tables():
     """[(weights, launches)] of every (kernel, grid) the adaptive cut has seen: relative share per CTA."""
     out = []
@@ -412,4 +417,4 @@ class PagedKVCache:
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
            "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused",
-           "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_tables"]
+           "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_refresh", "adaptive_cut_tables"]

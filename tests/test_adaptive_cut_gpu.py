@@ -80,3 +80,61 @@ def test_adaptive_cut_keeps_parity_while_shares_move(dtype, B, L, torch_cuda, pa
     again = steps(1, layers=1)[-1]
     assert torch.equal(again, fixed)
     cache.close()
+
+
+@pytest.mark.parametrize("dtype,B,L,hq", [(1, 96, 4096, 32), (0, 64, 4096, 32)])
+def test_device_planner_follows_the_adaptive_shares(dtype, B, L, hq, torch_cuda, pa):
+    """Plans cut on the device read the same weights: once the host has seen usable rates, the fetched
+    device plan is the cut of make_plan_weighted for those weights, bit for bit, and outputs stay within
+    rounding distance of the equal-share result."""
+    torch = torch_cuda
+    hkv = 8
+    pages = (L + 15) // 16
+    scale = 4.0 / 448.0 if dtype == 1 else 1.0
+    cfg = pa.PagedKVCache.Config(num_pages=B * pages, page_size=16, num_kv_heads=hkv, head_dim=128, max_slots=B,
+                                 max_pages_per_slot=pages, dtype=pa.KVDtype(dtype), k_scale=scale, v_scale=scale)
+    cache = pa.PagedKVCache(cfg)
+    cache.shuffle_free_pages(3)
+    K, V = seeded_kv([L], hkv, 128, 6)
+    dK = torch.from_numpy(K[0].view(np.int16)).cuda().view(torch.float16)
+    dV = torch.from_numpy(V[0].view(np.int16)).cuda().view(torch.float16)
+    for b in range(B):
+        assert cache.admit() == b and cache.append(b, dK, dV, L)
+    q = torch.randn(B, hq, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(5)).cuda()
+    before = pa.head_fused()
+    pa.set_head_fused(0)                                   # one schedule, so that fetch() shows the plan that ran
+    try:
+        pa.adaptive_cut_reset()
+        out = torch.zeros_like(q)
+        cache.plan_device(B, hq)
+        cache.run(q, out)
+        torch.cuda.synchronize()
+        fixed = out.clone()                                # adaptive cut off (fixture): equal shares
+        pa.set_adaptive_cut(True)
+        for _ in range(10):
+            cache.plan_device(B, hq)
+            for _ in range(3):
+                cache.run(q, out)
+        torch.cuda.synchronize()
+        assert pa.kernel_status() == 0
+        assert (out.float() - fixed.float()).abs().max().item() <= 2.5e-4
+        # the plan of one more step against the host's weighted planner with the weights of this moment
+        dp = pa.DevicePlan()
+        d_lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+        dp.build(dtype, d_lens, B, hq, hkv, 128, 0)
+        plan = dp.fetch()
+        tables = [w for w, launches in pa.adaptive_cut_tables() if launches > 0 and len(w) == plan.num_ctas]
+        moved = [w for w in tables if float(np.abs(w - 1.0).max()) > 0]
+        if moved:                                          # rates were usable (they are on any real GPU)
+            want = pa.make_plan_weighted(plan.tile, [L] * B, hq, hkv, moved[0])
+            assert (plan.segments == want.segments).all()
+            assert (plan.cta_seg_begin == want.cta_seg_begin).all()
+            assert (plan.item_seg_begin == want.item_seg_begin).all()
+        pa.adaptive_cut_reset()
+        dp.build(dtype, d_lens, B, hq, hkv, 128, 0)
+        equal = pa.make_plan(pa.KVDtype(dtype), [L] * B, hq, hkv, 128, 0)
+        again = dp.fetch()
+        assert (again.segments == equal.segments).all() and again.num_ctas == equal.num_ctas
+    finally:
+        pa.set_head_fused(before)
+    cache.close()
