@@ -39,10 +39,15 @@ std::mutex g_rate_mutex;
 std::unordered_map<RateKey, RateTable, RateKeyHash> g_rates;
 
 // The table of (this device, kernel, grid); created on first use.  Pointers into the map stay valid.
-RateTable* rate_table(const void* fn, int grid) {
+// create = false (a stream capture is under way: nothing may be allocated): only an existing table.
+RateTable* rate_table(const void* fn, int grid, bool create = true) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || grid <= 0) return nullptr;
     std::lock_guard<std::mutex> lock(g_rate_mutex);
+    if (!create) {
+        auto it = g_rates.find(RateKey{dev, fn, grid});
+        return it == g_rates.end() || !it->second.slots ? nullptr : &it->second;
+    }
     RateTable& t = g_rates[RateKey{dev, fn, grid}];
     if (!t.slots) {
         const size_t bytes = sizeof(unsigned long long) * (2 * grid + 1);   // + launches so far

@@ -899,7 +899,7 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess) { cudaGetLastError(); capture = cudaStreamCaptureStatusActive; }
     const bool capturing = capture != cudaStreamCaptureStatusNone;
     if (g_adaptive && batch > 0) {
-        if (RateTable* t = rate_table(k->fn, grid)) {
+        if (RateTable* t = rate_table(k->fn, grid, !capturing)) {
             if (!capturing) update_weights(t, stream);
             job.shares = t->shares;
             dp->stats = t->slots;
@@ -931,7 +931,7 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         fj.info = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + 2 * frow_bytes);
         fj.partial_lse = f.partial_out + frows * head_dim;
         if (g_adaptive && batch > 0) {
-            if (RateTable* t = rate_table(fk->fn, fgrid)) {
+            if (RateTable* t = rate_table(fk->fn, fgrid, !capturing)) {
                 if (!capturing) update_weights(t, stream);
                 fj.shares = t->shares;
                 f.stats = t->slots;

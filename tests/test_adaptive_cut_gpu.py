@@ -138,3 +138,64 @@ def test_device_planner_follows_the_adaptive_shares(dtype, B, L, hq, torch_cuda,
     finally:
         pa.set_head_fused(before)
     cache.close()
+
+
+def test_captured_step_follows_refreshed_shares(torch_cuda, pa):
+    """{device plan, decode} captured once in a CUDA graph with the adaptive cut on; between replays the
+    host folds new readings in with adaptive_cut_refresh, and the replayed plan follows them."""
+    torch = torch_cuda
+    B, L, hq, hkv = 64, 4096, 32, 8
+    pages = (L + 15) // 16
+    cfg = pa.PagedKVCache.Config(num_pages=B * pages, page_size=16, num_kv_heads=hkv, head_dim=128, max_slots=B,
+                                 max_pages_per_slot=pages, dtype=pa.KVDtype.FP16)
+    cache = pa.PagedKVCache(cfg)
+    cache.shuffle_free_pages(9)
+    K, V = seeded_kv([L], hkv, 128, 12)
+    dK = torch.from_numpy(K[0].view(np.int16)).cuda().view(torch.float16)
+    dV = torch.from_numpy(V[0].view(np.int16)).cuda().view(torch.float16)
+    for b in range(B):
+        assert cache.admit() == b and cache.append(b, dK, dV, L)
+    q = torch.randn(B, hq, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(8)).cuda()
+    out = torch.zeros_like(q)
+    d_lens = torch.full((B,), L, dtype=torch.int32, device="cuda")
+    p = cache.params()
+    p.seq_lens, p.q, p.out, p.batch, p.num_q_heads = d_lens.data_ptr(), q.data_ptr(), out.data_ptr(), B, hq
+    before = pa.head_fused()
+    pa.set_head_fused(0)
+    try:
+        pa.adaptive_cut_reset()
+        dp = pa.DevicePlan()
+        dp.build(0, d_lens, B, hq, hkv, 128, 0)
+        dp.bind(p)
+        pa.paged_decode(pa.KVDtype.FP16, p, 0, cfg.num_pages)       # equal shares (fixture: adaptive cut off)
+        torch.cuda.synchronize()
+        fixed = out.clone()
+        pa.set_adaptive_cut(True)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            dp.build(0, d_lens, B, hq, hkv, 128, 0, stream=side.cuda_stream)   # tables and buffers exist before the capture
+            dp.bind(p)
+            pa.paged_decode(pa.KVDtype.FP16, p, side.cuda_stream, cfg.num_pages)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                s = torch.cuda.current_stream().cuda_stream
+                dp.build(0, d_lens, B, hq, hkv, 128, 0, stream=s)
+                dp.bind(p)
+                pa.paged_decode(pa.KVDtype.FP16, p, s, cfg.num_pages)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(12):
+            pa.adaptive_cut_refresh()
+            graph.replay()
+        torch.cuda.synchronize()
+        assert pa.kernel_status() == 0
+        assert (out.float() - fixed.float()).abs().max().item() <= 2.5e-4
+        plan = dp.fetch()
+        moved = [w for w, n in pa.adaptive_cut_tables() if n > 0 and len(w) == plan.num_ctas and float(np.abs(w - 1).max()) > 0]
+        if moved:
+            want = pa.make_plan_weighted(plan.tile, [L] * B, hq, hkv, moved[0])
+            assert (plan.segments == want.segments).all() and (plan.cta_seg_begin == want.cta_seg_begin).all()
+    finally:
+        pa.set_head_fused(before)
+    cache.close()
