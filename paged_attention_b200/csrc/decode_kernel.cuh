@@ -983,13 +983,73 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 // with one warp per (row, head) such a merge was a third of a single-sequence decode step.
 // ROW_ITEMS = true: the plan's work items are rows (head-fused tiles).
 constexpr int MERGE_WIDE_MIN = 8;
-template<int GROUP, bool ROW_ITEMS = false>
+// One (row, query head) pair by the four warps of a CTA; s0, s1: the pair's segment range.
+template<int GROUP, bool ROW_ITEMS>
+__device__ __forceinline__ void merge_pair(const pd_params& p, int idx, int s0, int s1, float4 (*part_num)[32], float* part_den)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
+    if (s1 - s0 <= 1) return;   // written directly by the decode kernel
+    if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) return;   // merged by the decode kernel
+    GatherOut local{};   // world = 0: plain output
+    const int stride = ROW_ITEMS ? p.num_q_heads : GROUP;
+    const int gq     = ROW_ITEMS ? hq : hq % GROUP;
+    if (s1 - s0 <= MERGE_WIDE_MIN) {
+        if (warp == 0) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, stride, gq);
+        return;
+    }
+    float lse_max = -INFINITY;
+    for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * stride + gq));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    for (int base = s0 + warp; base < s1; base += 16) {
+        float  w[4];
+        float4 o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int s = base + 4 * j;
+            const bool live = s < s1;
+            w[j] = live ? exp2f(__ldcg(p.partial_lse + s * stride + gq) - lse_max) : 0.f;
+            o[j] = live ? __ldcg(reinterpret_cast<const float4*>(
+                              p.partial_out + (static_cast<size_t>(s) * stride + gq) * HEAD_DIM + lane * 4))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            num.x = fmaf(w[j], o[j].x, num.x); num.y = fmaf(w[j], o[j].y, num.y);
+            num.z = fmaf(w[j], o[j].z, num.z); num.w = fmaf(w[j], o[j].w, num.w);
+            den += w[j];
+        }
+    }
+    part_num[warp][lane] = num;
+    if (lane == 0) part_den[warp] = den;
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 1; w < 4; w++) {
+        const float4 other = part_num[w][lane];
+        num.x += other.x; num.y += other.y; num.z += other.z; num.w += other.w;
+        den += part_den[w];
+    }
+    const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
+    const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+    store_out(p, local, out_index(p, local, b, hq) + lane * 4, packed);
+}
+
+// WALK = false: one CTA per pair (grid = pairs).  WALK = true: a capped grid whose CTAs walk their pairs;
+// used when there are thousands of pairs, which is where this kernel is launched although almost every
+// pair is done after reading two integers (plans cut on the device).
+template<int GROUP, bool ROW_ITEMS = false, bool WALK = false>
 __global__ void __launch_bounds__(128)
 merge_segments_kernel(const __grid_constant__ pd_params p)
 {
     __shared__ float4 part_num[4][32];
     __shared__ float  part_den[4];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pairs = p.batch * p.num_q_heads;
     auto item_of = [&](int idx) {
         const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
@@ -998,71 +1058,20 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     // Launched as a programmatic dependent of the decode kernel: the CTAs may already be resident while
     // the decode kernel drains.  The plan arrays were written before that kernel started, so the first
     // pair's bounds are fetched ahead of the wait; everything else read below is that kernel's output.
-    int first0 = 0, first1 = 0;
+    int s0 = 0, s1 = 0;
     if (static_cast<int>(blockIdx.x) < pairs) {
-        first0 = p.item_seg_begin[item_of(blockIdx.x)];
-        first1 = p.item_seg_begin[item_of(blockIdx.x) + 1];
+        s0 = p.item_seg_begin[item_of(blockIdx.x)];
+        s1 = p.item_seg_begin[item_of(blockIdx.x) + 1];
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // The grid is capped (a few CTAs per SM); a CTA walks its (row, query head) pairs.  In the mode where
-    // this kernel is always launched almost every pair is done after reading two integers.
-    for (int idx = blockIdx.x; idx < pairs; idx += gridDim.x) {
-        const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
-        const int item = item_of(idx);
-        const int s0 = idx == static_cast<int>(blockIdx.x) ? first0 : p.item_seg_begin[item];
-        const int s1 = idx == static_cast<int>(blockIdx.x) ? first1 : p.item_seg_begin[item + 1];
-        if (s1 - s0 <= 1) continue;   // written directly by the decode kernel
-        if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) continue;   // merged by the decode kernel
-        GatherOut local{};   // world = 0: plain output
-        const int stride = ROW_ITEMS ? p.num_q_heads : GROUP;
-        const int gq     = ROW_ITEMS ? hq : hq % GROUP;
-        if (s1 - s0 <= MERGE_WIDE_MIN) {
-            if (warp == 0) merge_one_head<GROUP>(p, local, b, hq, s0, s1, lane, stride, gq);
-            continue;
+    if (static_cast<int>(blockIdx.x) >= pairs) return;
+    merge_pair<GROUP, ROW_ITEMS>(p, blockIdx.x, s0, s1, part_num, part_den);
+    if constexpr (WALK) {
+        for (int idx = blockIdx.x + gridDim.x; idx < pairs; idx += gridDim.x) {
+            __syncthreads();   // the scratch is reused
+            merge_pair<GROUP, ROW_ITEMS>(p, idx, p.item_seg_begin[item_of(idx)], p.item_seg_begin[item_of(idx) + 1],
+                                         part_num, part_den);
         }
-        float lse_max = -INFINITY;
-        for (int s = s0 + lane; s < s1; s += 32) lse_max = fmaxf(lse_max, __ldcg(p.partial_lse + s * stride + gq));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) lse_max = fmaxf(lse_max, __shfl_xor_sync(0xffffffffu, lse_max, o));
-        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-        float den = 0.f;
-        for (int base = s0 + warp; base < s1; base += 16) {
-            float  w[4];
-            float4 o[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int s = base + 4 * j;
-                const bool live = s < s1;
-                w[j] = live ? exp2f(__ldcg(p.partial_lse + s * stride + gq) - lse_max) : 0.f;
-                o[j] = live ? __ldcg(reinterpret_cast<const float4*>(
-                                  p.partial_out + (static_cast<size_t>(s) * stride + gq) * HEAD_DIM + lane * 4))
-                            : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                num.x = fmaf(w[j], o[j].x, num.x); num.y = fmaf(w[j], o[j].y, num.y);
-                num.z = fmaf(w[j], o[j].z, num.z); num.w = fmaf(w[j], o[j].w, num.w);
-                den += w[j];
-            }
-        }
-        part_num[warp][lane] = num;
-        if (lane == 0) part_den[warp] = den;
-        __syncthreads();
-        if (warp == 0) {
-#pragma unroll
-            for (int w = 1; w < 4; w++) {
-                const float4 other = part_num[w][lane];
-                num.x += other.x; num.y += other.y; num.z += other.z; num.w += other.w;
-                den += part_den[w];
-            }
-            const __half2 lo = __floats2half2_rn(num.x / den, num.y / den);
-            const __half2 hi = __floats2half2_rn(num.z / den, num.w / den);
-            uint2 packed;
-            packed.x = *reinterpret_cast<const uint32_t*>(&lo);
-            packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-            store_out(p, local, out_index(p, local, b, hq) + lane * 4, packed);
-        }
-        __syncthreads();   // the scratch is reused by this CTA's next pair
     }
 }
 

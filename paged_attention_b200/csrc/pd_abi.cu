@@ -93,10 +93,11 @@ void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap&
 // The merge kernel is launched as a programmatic dependent of the decode kernel before it: its CTAs are
 // placed while the decode grid drains and wait inside the kernel (griddepcontrol.wait) until that grid is
 // complete, which takes the launch latency out of the gap between the two kernels.
+constexpr int MERGE_GRID_CAP = 148 * 8;
 template<typename Kernel>
 void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_t stream) {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(std::min(blocks, 148 * 8)));   // the kernel walks its pairs
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
     cfg.blockDim = dim3(128);
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
@@ -108,7 +109,9 @@ void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_
 }
 template<int GROUP>
 void launch_merge(const pd_params& p, cudaStream_t stream) {
-    launch_dependent(pdk::merge_segments_kernel<GROUP, false>, p.batch * p.num_q_heads, p, stream);
+    const int pairs = p.batch * p.num_q_heads;
+    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, false, true>, MERGE_GRID_CAP, p, stream);
+    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, false, false>, pairs, p, stream);
 }
 
 template<typename KV, int GROUP, int V>
@@ -143,7 +146,9 @@ template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>;
 
 template<int GROUP>
 void launch_merge_rows(const pd_params& p, cudaStream_t stream) {
-    launch_dependent(pdk::merge_segments_kernel<GROUP, true>, p.batch * p.num_q_heads, p, stream);
+    const int pairs = p.batch * p.num_q_heads;
+    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, true, true>, MERGE_GRID_CAP, p, stream);
+    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, true, false>, pairs, p, stream);
 }
 
 template<typename KV, int GROUP>
