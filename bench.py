@@ -13,7 +13,11 @@ is sharded, every rank holds its own full-size layer shard (weak scaling) and th
 outputs are gathered inside the timed step - by default by the decode kernel itself
 (peer stores into every rank's buffer, `--gather peer`), or by ncclAllGather
 (`--gather nccl`); `--shard heads` splits the KV heads of one fixed problem instead
-(strong scaling, workload c5).
+(strong scaling, workload c5).  After the timed region every rank checks its gathered
+buffer bit for bit against an NCCL all-gather of the ranks' local outputs and two
+sampled rows against the CPU oracle (`gather_check`), and the 70B-shaped layer with
+its KV heads sharded over the same ranks is measured in the same process group
+(`c5_heads`, strong scaling against the unsharded layer on one GPU).
 
 `--impl reference` times the reference's own CPU attention (compiled from its
 sources into oracle/_ref, else the oracle port) on a bounded sample of the same
@@ -42,7 +46,12 @@ WORKLOADS = {
     "small": (0, 8, 8192, 32, 8, 16, "profiling case: batch 8 x 8192 fp16 (268 MB of KV, larger than L2)"),
     "small-fp8": (1, 16, 8192, 32, 8, 16, "profiling case: batch 16 x 8192 fp8 (268 MB of KV)"),
     "small-wide": (0, 64, 1024, 32, 8, 16, "profiling case of the head-fused schedule: batch 64 x 1024 fp16 (268 MB of KV)"),
+    "single": (0, 1, 16384, 32, 8, 16, "profiling case of the merge kernel: one sequence of 16384 tokens spread over the grid"),
 }
+DTYPE_NAMES = {0: "f16", 1: "f8e4m3"}
+ARITHMETIC = {0: "mma.m16n8k16 f16 x f16 -> f32 accumulate, softmax in f32; KV stored as fp16",
+              1: "mma.m16n8k32 e4m3 x e4m3 -> f32 accumulate on the stored bytes (fp16 queries and fp16-rounded softmax "
+                 "weights split exactly into three e4m3 terms), softmax in f32; KV stored as fp8 e4m3"}
 
 
 def algorithmic_bytes(dtype, lens, hq, hkv, page, d=128):
@@ -111,10 +120,17 @@ def measured_peak():
 # reference arm / CPU baseline: the reference's cpu_attention over a bounded sample
 # ---------------------------------------------------------------------------------------------
 
+def checker():
+    """The CPU oracle's ctypes wrapper (tests/oracle_lib.py): checker and CPU baseline only, never on the
+    measured path."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    return oracle_lib
+
+
 def cpu_sample_inputs(dtype, rows, L, hq, hkv, page, seed=7):
     """Host-side paged cache for `rows` sequences of length L, N(0,1) fp16 values, scattered pages."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import oracle_lib as ol
+    ol = checker()
     rng = np.random.default_rng(seed)
     pages = (L + page - 1) // page
     perm = rng.permutation(rows * pages).astype(np.int32).reshape(rows, pages)
@@ -132,8 +148,7 @@ def cpu_sample_inputs(dtype, rows, L, hq, hkv, page, seed=7):
 
 def run_cpu_attention(dtype, q, kc, vc, bt, lens, hq, hkv, page, scale, threads):
     """Returns (seconds of attention calls, kind, out) using oracle/_ref when present, else the oracle port."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import oracle_lib as ol
+    ol = checker()
     rows = q.shape[0]
     out = np.zeros((rows, hq, 128), np.float32)
     lens_a = np.ascontiguousarray(lens, np.int32)
@@ -155,10 +170,13 @@ def run_cpu_attention(dtype, q, kc, vc, bt, lens, hq, hkv, page, scale, threads)
 
 
 def cpu_leg(dtype, L, hq, hkv, page, batch, target_seconds=10.0):
-    """Times the CPU attention on a bounded sample: calibrates on one row, then sizes the sample."""
+    """Times the CPU attention on a bounded sample: calibrates on one row, then sizes the sample.  Also one
+    sequence x all query heads on a single thread, which is how the reference itself runs cpu_attention."""
     cores = os.cpu_count() or 1
     q, kc, vc, bt, scale = cpu_sample_inputs(dtype, 1, L, hq, hkv, page)
     t1, kind, _ = run_cpu_attention(dtype, q, kc, vc, bt, [L], hq, hkv, page, scale, cores)
+    t_single, _, _ = run_cpu_attention(dtype, q, kc, vc, bt, [L], hq, hkv, page, scale, 1)
+    one_row_bytes = algorithmic_bytes(dtype, [L], hq, hkv, page)
     rows = int(max(1, min(batch, target_seconds / max(t1, 1e-6))))
     reps = 1
     if rows > 1:
@@ -172,11 +190,13 @@ def cpu_leg(dtype, L, hq, hkv, page, batch, target_seconds=10.0):
     else:
         secs = t1
     nbytes = algorithmic_bytes(dtype, [L] * rows, hq, hkv, page)
+    what = "cpu_attention from the reference sources" if kind == "reference" else "oracle port of cpu_attention"
     return {"value": nbytes / secs / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
             "sample": f"{rows} of {batch} sequences x {hq} q heads at length {L} "
-                      f"({'cpu_attention from the reference sources' if kind == 'reference' else 'oracle port of cpu_attention'}, "
-                      f"OpenMP over (row, q head), gather excluded, {secs:.2f} s per pass, mean of {reps} passes)",
-            "seconds": secs, "rows": rows}
+                      f"({what}, OpenMP over (row, q head), gather excluded, {secs:.2f} s per pass, mean of {reps} passes)",
+            "single_thread": {"value": one_row_bytes / t_single / 1e9, "unit": "GB/s", "cores": 1,
+                              "sample": f"1 of {batch} sequences x {hq} q heads at length {L} on one thread, as the reference "
+                                        f"runs it ({t_single:.3f} s; the whole layer would take {t_single * batch:.1f} s)"}}
 
 
 def reference_arm(args, wl):
@@ -214,6 +234,188 @@ def reference_arm(args, wl):
 # our arm
 # ---------------------------------------------------------------------------------------------
 
+class _Dev:
+    """Zero-copy torch view of raw device memory."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+class Layer:
+    """One decode layer resident on this GPU: a cache filled with seeded N(0,1) tokens in scattered pages, the
+    query rows, an output buffer, and the plan, driven through the plan API as a serving engine does (plan
+    once per step, run per layer)."""
+
+    def __init__(self, torch, pa, dtype, B, L, hq, hkv, page, seed, stream, contiguous=False, ctas=0, shared_source=False):
+        self.torch, self.pa = torch, pa
+        self.dtype, self.B, self.L, self.hq, self.hkv, self.page, self.stream = dtype, B, L, hq, hkv, page, stream
+        self.group = hq // hkv
+        self.lens = [L] * B
+        pages = (L + page - 1) // page
+        self.scale = 5.0 / 448.0 if dtype == 1 else 1.0
+        self.cfg = pa.PagedKVCache.Config(num_pages=pages * B, page_size=page, num_kv_heads=hkv, head_dim=128, max_slots=B,
+                                          max_pages_per_slot=pages, dtype=pa.KVDtype(dtype), k_scale=self.scale,
+                                          v_scale=self.scale)
+        self.cache = pa.PagedKVCache(self.cfg)
+        if not contiguous:
+            self.cache.shuffle_free_pages(42)
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        k = v = None
+        for b in range(B):
+            if k is None or not shared_source:      # shared_source: every slot gets the same tokens (as the reference's bench does)
+                k = torch.randn(L, hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
+                v = torch.randn(L, hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
+            slot = self.cache.admit()
+            if not self.cache.append(slot, k, v, L, stream):
+                raise SystemExit("bench.py: pool out of pages")
+        del k, v
+        self.q_host = torch.randn(B, hq, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(seed + 99)).pin_memory()
+        self.out_host = torch.empty_like(self.q_host).pin_memory()
+        self.q = self.q_host.cuda()
+        self.out = torch.zeros_like(self.q)
+        self.plan = pa.make_plan(pa.KVDtype(dtype), self.lens, hq, hkv, 128, ctas)
+        self.dplan = pa.DevicePlan()
+        self.params = self.cache.params()
+        self.params.q, self.params.out = self.q.data_ptr(), self.out.data_ptr()
+        self.params.batch, self.params.num_q_heads = B, hq
+        self.replan()
+        self.bytes = algorithmic_bytes(dtype, self.lens, hq, hkv, page)
+
+    def replan(self):
+        self.dplan.upload(self.plan, self.group, 128, self.stream)
+        self.dplan.bind(self.params)
+
+    def decode(self):
+        self.pa.paged_decode(self.pa.KVDtype(self.dtype), self.params, self.stream, self.cfg.num_pages)
+
+    def launch(self):
+        return self.pa.describe_launch(self.pa.KVDtype(self.dtype), self.params)
+
+    def oracle_rows(self, rows):
+        """Checker: the oracle's output for a few rows, from the cache bytes as stored on the device."""
+        ol = checker()
+        torch, cfg = self.torch, self.cfg
+        elem = 2 if self.dtype == 0 else 1
+        page_elems = self.hkv * self.page * 128
+        t_dt, n_dt = (torch.float16, np.uint16) if self.dtype == 0 else (torch.uint8, np.uint8)
+        nbytes = cfg.num_pages * page_elems * elem
+        kpool = torch.as_tensor(_Dev(self.params.k_cache, nbytes), device="cuda").view(t_dt).view(cfg.num_pages, page_elems)
+        vpool = torch.as_tensor(_Dev(self.params.v_cache, nbytes), device="cuda").view(t_dt).view(cfg.num_pages, page_elems)
+        pages = (self.L + self.page - 1) // self.page
+        out = {}
+        for row in rows:
+            table = torch.from_numpy(self.cache.block_table(row).astype(np.int64)).cuda()
+            kc = kpool[table].cpu().numpy().view(n_dt).reshape(-1)
+            vc = vpool[table].cpu().numpy().view(n_dt).reshape(-1)
+            q = self.q[row:row + 1].cpu().numpy()
+            out[row] = ol.paged_decode(1, self.dtype, q.view(np.uint16), kc, vc, np.arange(pages, dtype=np.int32)[None],
+                                       [self.L], self.hq, self.hkv, 128, self.page, k_scale=self.scale, v_scale=self.scale)[0]
+        return out
+
+    def close(self):
+        self.cache.close()
+
+
+class Gather:
+    """Output gather of one sharded layer: peer stores by the decode kernel, or ncclAllGather."""
+
+    def __init__(self, torch, pa, dist, layer, shard, mode, world, rank):
+        self.torch, self.pa, self.dist, self.layer, self.shard, self.world, self.rank = torch, pa, dist, layer, shard, world, rank
+        self.rows_total = layer.B if shard == "heads" else layer.B * world
+        self.heads_total = layer.hq * world if shard == "heads" else layer.hq
+        self.full_bytes = self.rows_total * self.heads_total * 128 * 2
+        self.head_off = rank * layer.hq if shard == "heads" else 0
+        self.row_off = 0 if shard == "heads" else rank * layer.B
+        self.note = None
+        self.gg = None
+        self.mode = mode
+        if mode == "peer":
+            # Peer stores need CUDA IPC mappings between all GPUs of the node.  If any rank cannot set them
+            # up, every rank falls back to ncclAllGather (and the JSON line says so).
+            from paged_attention_b200.sharding import GatherGroup
+            ok = torch.ones(1, device="cuda")
+            try:
+                self.gg = GatherGroup(self.full_bytes)
+            except Exception as e:
+                ok.zero_()
+                self.note = "peer setup failed (%s); fell back to ncclAllGather" % str(e)[:120]
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                if self.gg is not None:
+                    self.gg.close()
+                    self.gg = None
+                self.mode = "nccl"
+                self.note = self.note or "a peer could not set up IPC mappings; fell back to ncclAllGather"
+        if self.mode == "nccl":
+            self.gathered = torch.empty((world * layer.B, layer.hq, 128), dtype=torch.float16, device="cuda")
+        else:
+            self.views = [torch.as_tensor(_Dev(self.gg.buffer_ptr(i), self.full_bytes), device="cuda") for i in range(4)]
+            self.share = self.full_bytes // world      # each rank returns its 1/world of the gathered result to the host
+            self.full_host = torch.empty(self.share, dtype=torch.uint8).pin_memory()
+        self.first_epoch = None
+
+    def decode(self):
+        """One layer with its rows stored into every rank's buffer; does not wait for the peers' rows."""
+        ly = self.layer
+        if self.mode == "peer":
+            self.gg.decode(self.pa.KVDtype(ly.dtype), ly.params, self.heads_total, self.head_off, self.row_off, ly.stream,
+                           ly.cfg.num_pages)
+        else:
+            ly.decode()
+            self.dist.all_gather_into_tensor(self.gathered, ly.out)
+
+    def wait(self, back=0):
+        """Wait (bounded, on the stream) until every rank's rows of the step `back` steps ago have landed."""
+        if self.mode == "peer":
+            self.gg.wait_epoch(self.gg.epoch - back, self.layer.stream)
+
+    def last_view(self):
+        """The gathered result of the last step as a [rows][heads][128] fp16 tensor, in the full layout."""
+        torch = self.torch
+        if self.mode == "peer":
+            return self.views[self.gg.epoch % 4].view(torch.float16).view(self.rows_total, self.heads_total, 128)
+        g = self.gathered
+        if self.shard == "heads":
+            return g.view(self.world, self.layer.B, self.layer.hq, 128).permute(1, 0, 2, 3).reshape(self.rows_total, self.heads_total, 128)
+        return g
+
+    def check(self):
+        """After the timed region: this rank's gathered buffer against an NCCL all-gather of the ranks' local
+        outputs of the same plan (bit for bit), and two of this rank's rows against the CPU oracle."""
+        torch, dist, ly = self.torch, self.dist, self.layer
+        self.decode()
+        self.wait()
+        torch.cuda.synchronize()
+        got = self.last_view().clone()
+        ly.out.zero_()
+        ly.decode()                                   # local output of the same device plan
+        parts = torch.empty((self.world * ly.B, ly.hq, 128), dtype=torch.float16, device="cuda")
+        dist.all_gather_into_tensor(parts, ly.out)
+        if self.shard == "heads":
+            want = parts.view(self.world, ly.B, ly.hq, 128).permute(1, 0, 2, 3).reshape(self.rows_total, self.heads_total, 128)
+        else:
+            want = parts
+        equal = bool(torch.equal(got, want))
+        rows = (0, ly.B - 1)
+        oracle = ly.oracle_rows(rows)
+        worst = 0.0
+        for row, w in oracle.items():
+            mine = got[row + self.row_off, self.head_off:self.head_off + ly.hq].float().cpu().numpy()
+            worst = max(worst, float(np.abs(mine - w).max()))
+        flags = torch.tensor([1.0 if equal else 0.0, -worst], device="cuda")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        all_equal, all_worst = bool(flags[0].item() == 1.0), float(-flags[1].item())
+        return {"ok": all_equal and all_worst <= 2e-3, "bit_exact_vs_nccl_all_gather": all_equal,
+                "max_abs_vs_oracle": all_worst, "tolerance": 2e-3,
+                "checked": "every rank: its whole gathered buffer vs ncclAllGather of the local outputs; rows %s of its shard vs the CPU oracle"
+                           % (list(rows),)}
+
+    def close(self):
+        if self.gg is not None:
+            self.dist.barrier()
+            self.gg.close()
+
+
 def our_arm(args, wl):
     import torch
     import paged_attention_b200 as pa
@@ -230,248 +432,245 @@ def our_arm(args, wl):
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    if args.variant is not None:
-        pa.set_kernel_variant(args.variant)
     if args.workload == "small-wide":
         pa.set_head_fused(2)      # the profiling case of the head-fused kernel is too short for it to be chosen by itself
-
-    shard = args.shard or ("heads" if args.workload == "c5" else "batch")
-    if shard == "heads":
-        if hkv % world or hq % world:
-            raise SystemExit("--shard heads needs the head counts to divide by the number of GPUs")
-        l_hq, l_hkv, l_B = hq // world, hkv // world, B
-        scaling = "strong"
-    else:
-        l_hq, l_hkv, l_B = hq, hkv, B          # every rank holds a full-size shard of the global batch
-        scaling = "weak"
-    group = l_hq // l_hkv
-    lens = [L] * l_B
-    pages = (L + page - 1) // page
-    scale = 5.0 / 448.0 if dtype == 1 else 1.0
-    cfg = pa.PagedKVCache.Config(num_pages=pages * l_B, page_size=page, num_kv_heads=l_hkv, head_dim=128,
-                                 max_slots=l_B, max_pages_per_slot=pages, dtype=pa.KVDtype(dtype), k_scale=scale,
-                                 v_scale=scale)
-    cache = pa.PagedKVCache(cfg)
-    if not args.contiguous_pages:
-        cache.shuffle_free_pages(42)
     stream = torch.cuda.current_stream().cuda_stream
-    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    for b in range(l_B):
-        k = torch.randn(L, l_hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
-        v = torch.randn(L, l_hkv, 128, device="cuda", dtype=torch.float16, generator=gen)
-        slot = cache.admit()
-        if not cache.append(slot, k, v, L, stream):
-            raise SystemExit("bench.py: pool out of pages")
-    del k, v
-    q_host = torch.randn(l_B, l_hq, 128, dtype=torch.float16, generator=torch.Generator().manual_seed(99 + rank)).pin_memory()
-    out_host = torch.empty_like(q_host).pin_memory()
-    q = q_host.cuda()
-    out = torch.zeros_like(q)
-    # N > 1: the outputs of all ranks are put together inside the step.  "peer" (default): the decode
-    # kernel stores its rows into every peer's gathered buffer and a one-warp kernel waits for the
-    # peers' flags; "nccl": decode into a local buffer, then ncclAllGather.
-    gather_mode = args.gather if world > 1 else "none"
-    gathered, gg, gathered_views = None, None, None
-    rows_total = l_B if shard == "heads" else l_B * world
-    heads_total = l_hq * world if shard == "heads" else l_hq
-    full_bytes = rows_total * heads_total * 128 * 2
-    gather_note = None
-    if gather_mode == "peer":
-        # Peer stores need CUDA IPC mappings between all GPUs of the node.  If any rank cannot set them
-        # up, every rank falls back to ncclAllGather (and the JSON line says so).
-        from paged_attention_b200.sharding import GatherGroup
-        ok = torch.ones(1, device="cuda")
-        try:
-            gg = GatherGroup(full_bytes)
-        except Exception as e:
-            ok.zero_()
-            gather_note = "peer setup failed (%s); fell back to ncclAllGather" % str(e)[:120]
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if ok.item() == 0:
-            if gg is not None:
-                gg.close()
-                gg = None
-            gather_mode = "nccl"
-            gather_note = gather_note or "a peer could not set up IPC mappings; fell back to ncclAllGather"
-    if gather_mode == "nccl":
-        gathered = torch.empty((world * l_B, l_hq, 128), dtype=out.dtype, device="cuda")
-    elif gather_mode == "peer":
-        head_off = rank * l_hq if shard == "heads" else 0
-        row_off = 0 if shard == "heads" else rank * l_B
-
-        class _Dev:   # zero-copy torch view of the library's gathered buffers
-            def __init__(self, ptr, n):
-                self.__cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
-        gathered_views = [torch.as_tensor(_Dev(gg.buffer_ptr(i), full_bytes), device="cuda") for i in (0, 1)]
-        share = full_bytes // world      # each rank returns its 1/world of the gathered result to the host
-        full_host = torch.empty(share, dtype=torch.uint8).pin_memory()
-
-    # Drive the kernel through the plan API, as a serving engine does: plan once per step, run per layer.
-    # During warm-up the plan is uploaded again before every step: that is what a serving loop does as
-    # lengths grow, and it is where the engine's adaptive cut takes in the per-CTA rates recorded by the
-    # launches before it.  The timed steps then run the plan of the last warm-up step.
-    plan = pa.make_plan(pa.KVDtype(dtype), lens, l_hq, l_hkv, 128, args.ctas)
-    dplan = pa.DevicePlan()
-    params = cache.params()
-    params.q, params.out = q.data_ptr(), out.data_ptr()
-    params.batch, params.num_q_heads = l_B, l_hq
-
-    def replan():
-        dplan.upload(plan, group, 128, stream)
-        dplan.bind(params)
-    replan()
-    needs_merge = params.needs_merge
 
     flush_buf = torch.zeros(512 << 20, dtype=torch.uint8, device="cuda")
 
     def flush():   # read-only pass over 4x L2: the next kernel starts cold and L2 holds no dirty lines
         pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)
 
-    step_counter = [0]
-
-    def step():
-        step_counter[0] += 1
-        if gather_mode == "peer":
-            gg.decode(pa.KVDtype(dtype), params, heads_total, head_off, row_off, stream, cfg.num_pages)
-            gg.wait(stream)
-            return
-        pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
-        if gather_mode == "nccl":
-            dist.all_gather_into_tensor(gathered, out)
-
-    def step_decode_only():
-        params.needs_merge = -1      # diagnostic value: decode kernel only, split rows stay unmerged
-        pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
-        params.needs_merge = needs_merge
-
-    def step_e2e():
-        q.copy_(q_host, non_blocking=True)
-        step()
-        if gather_mode == "peer":     # the gathered result comes back to the host once, one share per rank
-            full_host.copy_(gathered_views[step_counter[0] & 1][rank * share:(rank + 1) * share], non_blocking=True)
-        elif gather_mode == "nccl":
-            out_host.copy_(gathered[rank * l_B:(rank + 1) * l_B], non_blocking=True)
-        else:
-            out_host.copy_(out, non_blocking=True)
-
-    def step_e2e_direct():
-        # The same call with q and out pointing straight at the pinned host buffers: the kernel's own
-        # copy engine pulls each segment's query rows over PCIe and the epilogue stores go to host
-        # memory, so the transfers are inside the kernel (1 GPU only).
-        params.q, params.out = q_host.data_ptr(), out_host.data_ptr()
-        pa.paged_decode(pa.KVDtype(dtype), params, stream, cfg.num_pages)
-        params.q, params.out = q.data_ptr(), out.data_ptr()
-
     rendezvous = torch.zeros(1, device="cuda")
-
-    def timed(fn, steps):
-        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        for s, e in ev:
-            if args.replan_every_step:
-                replan()
-            flush()
-            if world > 1:      # device-side rendezvous: all ranks enter the step together, so one rank's
-                dist.all_reduce(rendezvous)   # slower flush is not charged to the others' step
-            s.record()
-            fn()
-            e.record()
-        torch.cuda.synchronize()
-        return [s.elapsed_time(e) for s, e in ev]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    # W warm-up steps as asked (at least 3), preceded by as many settling steps as it takes to make 24 in
-    # all: the adaptive cut needs about 20 plans to settle, as it would have in any serving loop
-    warmup = max(args.warmup, 3)
-    settle = max(0, 24 - warmup)
-    for _ in range(settle + warmup):
-        replan()
-        flush()
-        step()
-    barrier()
-    t_wall0 = time.perf_counter()
-    ms = timed(step, args.steps)
-    barrier()
-    wall = time.perf_counter() - t_wall0
-    ms_decode = timed(step_decode_only, args.steps)
-    ms_e2e = timed(step_e2e, args.steps)
-    ms_direct = timed(step_e2e_direct, args.steps) if world == 1 else None
-    if ms_direct is not None:      # the host buffer must hold the same result as the device path
+    def timed(fn, steps, before=None, after_last=None):
+        """Per step: flush (outside the events), ranks rendezvous, events around fn().  after_last runs inside
+        the last step's events.  Returns the per-step milliseconds of this rank."""
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i, (s, e) in enumerate(ev):
+            if before:
+                before()
+            flush()
+            if world > 1:      # device-side rendezvous: all ranks enter the step together, so one rank's
+                dist.all_reduce(rendezvous)   # slower flush is not charged to the others' step
+            s.record()
+            fn()
+            if after_last and i == steps - 1:
+                after_last()
+            e.record()
         torch.cuda.synchronize()
-        direct_ok = bool(torch.equal(out_host, out.cpu()))
+        return [s.elapsed_time(e) for s, e in ev]
+
+    def max_over_ranks(values):
+        t = torch.tensor(values, dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def measure(layer, gather, steps, warmup, settle_to=24):
+        """The step protocol for one layer (+ gather).  Returns a dict of per-step milliseconds (max over ranks)."""
+        if gather is None:
+            step, finish = layer.decode, None
+            strict = None
+        else:
+            # Pipelined by one step: step e's decode is launched before the wait for step e-1's rows, so the wait
+            # overlaps the decode; the last step's own rows are waited for inside its events.
+            def step():
+                gather.decode()
+                if gather.first_epoch is not None and gather.mode == "peer" and gather.gg.epoch > gather.first_epoch:
+                    gather.wait(back=1)
+
+            def finish():
+                gather.wait()
+
+            def strict():
+                gather.decode()
+                gather.wait()
+        # W warm-up steps as asked (at least 3), preceded by as many settling steps as it takes to make
+        # `settle_to` untimed steps in all: the adaptive cut folds in one reading per plan and needs about 20
+        # to settle, as it would have in any serving loop.  All of them are reported as warm-up.
+        untimed = max(max(warmup, 3), settle_to if pa.adaptive_cut() else 0)
+        for _ in range(untimed):
+            layer.replan()
+            flush()
+            (strict or step)()
+        barrier()
+        if gather is not None and gather.mode == "peer":
+            gather.first_epoch = gather.gg.epoch
+        t0 = time.perf_counter()
+        ms = timed(step, steps, before=layer.replan if args.replan_every_step else None, after_last=finish)
+        barrier()
+        wall = time.perf_counter() - t0
+        res = {"untimed": untimed, "wall": wall, "ms_list": ms}
+        res["ms_kernel"] = timed(layer.decode, steps)          # the decode (+ merge) alone, local output
+        if strict:
+            res["ms_strict"] = timed(strict, steps)
+        per = max_over_ranks([sum(ms) / steps, sum(res["ms_kernel"]) / steps, sum(res.get("ms_strict", ms)) / steps,
+                              statistics.median(ms)])
+        res["per_step"], res["per_kernel"], res["per_strict"], res["median"] = per
+        return res
+
+    # ---- the headline workload ------------------------------------------------------------------------------
+    shard = args.shard or ("heads" if args.workload == "c5" else "batch")
+    if shard == "heads":
+        if hkv % world or hq % world:
+            raise SystemExit("--shard heads needs the head counts to divide by the number of GPUs")
+        l_hq, l_hkv, scaling = hq // world, hkv // world, "strong"
+    else:
+        l_hq, l_hkv, scaling = hq, hkv, "weak"          # every rank holds a full-size shard of the global batch
+    layer = Layer(torch, pa, dtype, B, L, l_hq, l_hkv, page, 1234 + rank, stream, args.contiguous_pages, args.ctas,
+                  shared_source=args.workload == "c5")
+    gather = Gather(torch, pa, dist, layer, shard, args.gather, world, rank) if world > 1 else None
+    needs_merge = layer.params.needs_merge
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    m = measure(layer, gather, args.steps, args.warmup)
+
+    # end to end through host buffers: pinned q -> device, the step, result -> pinned host
+    def step_e2e():
+        layer.q.copy_(layer.q_host, non_blocking=True)
+        if gather is None:
+            layer.decode()
+            layer.out_host.copy_(layer.out, non_blocking=True)
+        else:
+            gather.decode()
+            gather.wait()
+            if gather.mode == "peer":     # the gathered result comes back to the host once, one share per rank
+                buf = gather.views[gather.gg.epoch % 4]
+                gather.full_host.copy_(buf[rank * gather.share:(rank + 1) * gather.share], non_blocking=True)
+            else:
+                layer.out_host.copy_(gather.gathered[rank * layer.B:(rank + 1) * layer.B], non_blocking=True)
+
+    def step_e2e_direct():
+        # The same call with q and out pointing straight at the pinned host buffers: the kernel's own
+        # copy engine pulls each segment's query rows over PCIe and the epilogue stores go to host
+        # memory, so the transfers are inside the kernel (1 GPU only).
+        layer.params.q, layer.params.out = layer.q_host.data_ptr(), layer.out_host.data_ptr()
+        layer.decode()
+        layer.params.q, layer.params.out = layer.q.data_ptr(), layer.out.data_ptr()
+
+    ms_e2e = timed(step_e2e, args.steps)
+    ms_direct, direct_ok = None, None
+    if world == 1:
+        ms_direct = timed(step_e2e_direct, args.steps)
+        torch.cuda.synchronize()           # the host buffer must hold the same result as the device path
+        layer.decode()
+        torch.cuda.synchronize()
+        direct_ok = bool(torch.equal(layer.out_host, layer.out.cpu()))
+    per_e2e = max_over_ranks([sum(ms_e2e) / args.steps])[0]
     barrier()
     clocks = sampler.stop() if sampler else None
     pa.kernel_status(stream)
 
-    total = torch.tensor([sum(ms), sum(ms_decode), sum(ms_e2e)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(total, op=dist.ReduceOp.MAX)
-    total = total.tolist()
-    per_step, per_decode, per_e2e = (t / args.steps for t in total)
+    # two layers back to back (no flush between them): strict = decode, wait, decode, wait; pipelined = decode,
+    # decode, wait, wait: the first layer's wait overlaps the second layer's decode
+    back_to_back = None
+    if gather is not None and gather.mode == "peer":
+        def two_strict():
+            gather.decode(); gather.wait(); gather.decode(); gather.wait()
 
-    local_bytes = algorithmic_bytes(dtype, lens, l_hq, l_hkv, page)
+        def two_pipelined():
+            gather.decode(); gather.decode(); gather.wait(back=1); gather.wait()
+        a = max_over_ranks([sum(timed(two_strict, args.steps)) / args.steps])[0]
+        b = max_over_ranks([sum(timed(two_pipelined, args.steps)) / args.steps])[0]
+        back_to_back = {"two_layers_strict_ms": a, "two_layers_pipelined_ms": b,
+                        "note": "events around two consecutive layers; pipelined launches the second decode before waiting for the first layer's rows"}
+
+    gather_check = gather.check() if gather is not None else None
+    launch = layer.launch()
+    per_step, per_kernel = m["per_step"], m["per_kernel"]
+    local_bytes = layer.bytes
     job_bytes = local_bytes * world
     value = job_bytes / (per_step * 1e-3) / 1e9
     e2e_value = job_bytes / (per_e2e * 1e-3) / 1e9
     peak, peak_src = measured_peak()
-    # The dominant kernel's launch duration: on one GPU with rows merged inside the decode kernel (or not
-    # split at all) a step IS one launch of that kernel; otherwise (separate merge kernel, or the output
-    # gather and its wait for peers inside the launch) the decode kernel is timed alone.
-    single_launch = world == 1 and needs_merge != 1
-    kernel_ms = per_step if single_launch else per_decode
-    achieved = local_bytes / (kernel_ms * 1e-3) / 1e9
+    merged_in_kernel = launch["merge"] != "merge kernel" and not launch["merge"].startswith("per row")
+    achieved = local_bytes / (per_kernel * 1e-3) / 1e9
+    one_row_check = None
+    if world == 1:
+        layer.decode()
+        torch.cuda.synchronize()
+        want = layer.oracle_rows((0, B - 1))
+        one_row_check = max(float(np.abs(layer.out[r].float().cpu().numpy() - w).max()) for r, w in want.items())
+
+    # ---- the reference's own GPU kernel on the same cache bytes (1 GPU; checker library, outside the timed region)
+    reference_gpu = None
+    if world == 1 and not args.no_reference_gpu:
+        reference_gpu = time_reference_kernel(torch, layer, flush, args.steps)
+
+    # ---- the 70B-shaped layer with its kv heads sharded over the same ranks (strong scaling) ----------------------
+    c5 = None
+    if args.workload != "c5" and not args.no_c5 and 8 % world == 0:
+        if gather is not None:
+            gather.close()
+            gather = None
+        layer.close()
+        c5 = c5_heads(torch, pa, dist, world, rank, stream, measure, max_over_ranks, args)
 
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             cpu = cpu_leg(dtype, L, hq, hkv, page, B)
-            cpu.pop("seconds", None)
-            cpu.pop("rows", None)
+        gather_mode = gather_mode_of(world, args, launch, gather_check)
         line = {
             "metric": "paged_decode_achieved_hbm_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warmup, "ms_per_step": per_step,
+            "steps": args.steps, "warmup": m["untimed"], "warmup_requested": args.warmup, "ms_per_step": per_step,
+            "ms_per_step_median": m["median"],
             "us_per_layer": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "f16",
+            "dtype": DTYPE_NAMES[dtype],
             "data": "synthetic",
-            "config": {"workload": desc, "name": args.workload,
-                       "arithmetic": "mma.m16n8k16 f16 x f16 -> f32 accumulate, softmax in f32; KV stored as %s"
-                                     % ("fp16" if dtype == 0 else "fp8 e4m3, widened to f16 in registers"), "batch_per_gpu": l_B, "seq_len": L, "q_heads_per_gpu": l_hq,
+            "config": {"workload": desc, "name": args.workload, "arithmetic": ARITHMETIC[dtype],
+                       "batch_per_gpu": B, "seq_len": L, "q_heads_per_gpu": l_hq,
                        "kv_heads_per_gpu": l_hkv, "page_size": page, "sharding": "none" if world == 1 else shard,
-                       "gather": {"none": "single GPU", "peer": "decode kernel stores into every peer's buffer (NVLink peer stores) + flag wait kernel",
-                                  "nccl": "ncclAllGather after the decode"}[gather_mode] + (" [" + gather_note + "]" if gather_note else ""),
+                       "gather": gather_mode,
                        "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
-                       "ctas": plan.num_ctas, "segments": plan.num_segments, "tile": plan.tile,
-                       "kernel_variant": pa.kernel_variant(),
-                       "plan": "uploaded before every warm-up step, timed steps reuse the last one; adaptive cut %s; %d settling steps before the warm-up"
-                               % ("on" if pa.adaptive_cut() else "off", settle),
+                       "plan_of_the_caller": {"ctas": layer.plan.num_ctas, "segments": layer.plan.num_segments, "tile": layer.plan.tile},
+                       "launch": launch,
+                       "plan": "uploaded before every untimed step, timed steps reuse the last one; adaptive cut %s"
+                               % ("on" if pa.adaptive_cut() else "off"),
                        "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
                              % (local_bytes / 1e6),
-                       "timing": "CUDA events around decode+merge%s per step, summed over steps, max over ranks"
-                                 % (" + output gather; ranks rendezvous (1-element all-reduce) after the flush, before the start event" if world > 1 else "")},
+                       "timing": "CUDA events around decode+merge%s per step, summed over steps (mean; median beside it), max over ranks"
+                                 % (" + output gather; ranks rendezvous (1-element all-reduce) after the flush, before the start "
+                                    "event; a step waits for the previous step's rows after launching its own decode and the last "
+                                    "step also for its own (strict order in ms_per_step_strict)" if world > 1 else "")},
             "algorithmic_bytes_per_step": job_bytes,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "kernel": "paged_decode_kernel",
-                         "kernel_ms": kernel_ms, "kernel_ms_without_merge": per_decode,
-                         "kernel_ms_source": "the step's single launch" if single_launch else "decode kernel timed alone",
+                         "kernel_ms": per_kernel,
+                         "kernel_ms_source": ("the decode launch timed alone with local output (split rows merged inside it)"
+                                              if merged_in_kernel else "decode + merge kernel timed alone with local output"),
                          "frac_of_8TBps_nominal": achieved / 8000.0},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": per_e2e,
-                    "h2d_bytes_per_step": q_host.numel() * 2,
-                    "d2h_bytes_per_step": full_bytes // world if gather_mode == "peer" else out_host.numel() * 2,
-                    "note": "pinned q -> device, decode+merge, out -> pinned host, per step; the KV cache is resident state"},
+                    "h2d_bytes_per_step": layer.q_host.numel() * 2,
+                    "d2h_bytes_per_step": layer.out_host.numel() * 2,
+                    "note": "pinned q -> device, decode+merge%s, result -> pinned host, per step; the KV cache is resident state"
+                            % (" + gather + wait, one 1/N share of the gathered result" if world > 1 else "")},
             "e2e_host_pointers": None if ms_direct is None else {
                 "value": job_bytes / (sum(ms_direct) / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                 "ms_per_step": sum(ms_direct) / args.steps, "matches_device_path": direct_ok,
                 "note": "same C-ABI call with q/out = pinned host pointers: query rows and outputs cross PCIe inside the kernel, no separate copies"},
-            "gpu_launches": args.steps * (2 + (1 if gather_mode == "peer" else 0) + (1 if needs_merge == 1 else 0)),
-            "gpu_launches_note": "per step: paged_decode_kernel (split rows merged in-kernel)%s%s + stream_read_kernel (L2 flush)"
-                                 % (" + merge_segments_kernel" if needs_merge == 1 else "",
-                                    " + gather_wait_kernel" if gather_mode == "peer" else ""),
-            "clocks": clocks, "wall_s_timed_region": wall,
+            "gpu_launches": args.steps * launches_per_step(world, args, launch),
+            "gpu_launches_note": "per step: paged_decode_kernel%s%s + stream_read_kernel (L2 flush)"
+                                 % ("" if merged_in_kernel else " + merge_segments_kernel",
+                                    " + gather_wait_kernel" if world > 1 and args.gather == "peer" else ""),
+            "clocks": clocks, "wall_s_timed_region": m["wall"],
         }
+        if world > 1:
+            line["ms_per_step_strict"] = m["per_strict"]
+            line["gather_check"] = gather_check
+            line["back_to_back"] = back_to_back
+        if one_row_check is not None:
+            line["oracle_check"] = {"max_abs_rows_0_and_last": one_row_check, "tolerance": 2e-3, "ok": one_row_check <= 2e-3}
+        if reference_gpu:
+            line["reference_gpu"] = reference_gpu
+        if c5:
+            line["c5_heads"] = c5
         if cpu:
             line["cpu_baseline"] = cpu
         traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
@@ -482,12 +681,135 @@ def our_arm(args, wl):
                 line["roofline"]["traffic"] = t["dram_bytes_per_launch"]
                 line["roofline"]["traffic_source"] = t["source"]
         print(json.dumps(line))
-    if gg is not None:
-        dist.barrier()
-        gg.close()
-    cache.close()
+    if gather is not None:
+        gather.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    if gather_check is not None and not gather_check["ok"]:
+        raise SystemExit("bench.py: the gathered output differs (gather_check)")
+
+
+def gather_mode_of(world, args, launch, gather_check):
+    if world == 1:
+        return "single GPU"
+    if args.gather == "peer":
+        return "decode kernel stores into every peer's buffer (16-byte NVLink peer stores) + flag wait kernel"
+    return "ncclAllGather after the decode"
+
+
+def launches_per_step(world, args, launch):
+    n = 2                                         # decode + L2 flush
+    if launch["merge"] == "merge kernel" or launch["merge"].startswith("per row"):
+        n += 1
+    if world > 1 and args.gather == "peer":
+        n += 1
+    return n
+
+
+def time_reference_kernel(torch, layer, flush, steps):
+    """The reference's paged_decode_kernel (mma.sync + cp.async), compiled for sm_100a from its own sources into
+    oracle/_ref, on the engine's cache bytes and block table: same flush + event protocol, outside the
+    headline's timed region (bench/bench_decode.cu:121-139,198-209 of the reference)."""
+    ol = checker()
+    R = ol.ref()
+    if R is None:
+        return {"unavailable": "oracle/_ref/libpd_ref.so is not built"}
+    p = layer.params
+    dec = R.ref_decoder_create()
+    lens = np.ascontiguousarray(layer.lens, np.int32)
+    ref_out = torch.zeros_like(layer.q)
+    if R.ref_decoder_plan(dec, layer.dtype, lens.ctypes.data_as(C.POINTER(C.c_int)), layer.B, layer.hq, layer.hkv, 128, 0) != 0:
+        return {"unavailable": R.ref_last_error().decode()}
+    pages = (layer.L + layer.page - 1) // layer.page
+
+    def run():
+        rc = R.ref_decoder_run(dec, layer.dtype, layer.q.data_ptr(), ref_out.data_ptr(), p.k_cache, p.v_cache, p.block_table,
+                               pages, p.seq_lens, layer.B, layer.hq, layer.hkv, 128, layer.page, layer.scale, layer.scale, None)
+        if rc != 0:
+            raise SystemExit("reference kernel: " + R.ref_last_error().decode())
+    for _ in range(5):
+        flush()
+        run()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s, e in ev:
+        flush()
+        s.record()
+        run()
+        e.record()
+    torch.cuda.synchronize()
+    ms = [s.elapsed_time(e) for s, e in ev]
+    layer.decode()
+    torch.cuda.synchronize()
+    ctas, segs = C.c_int(), C.c_int()
+    R.ref_decoder_info(dec, C.byref(ctas), C.byref(segs))
+    R.ref_decoder_destroy(dec)
+    mean = sum(ms) / len(ms)
+    return {"kernel": "the reference's paged_decode_kernel + merge_segments_kernel (mma.sync m16n8k16 + cp.async), its own sources "
+                      "compiled for sm_100a into oracle/_ref, on the engine's cache bytes and block table",
+            "us_per_layer": mean * 1e3, "us_per_layer_median": statistics.median(ms) * 1e3,
+            "value": layer.bytes / (mean * 1e-3) / 1e9, "unit": "GB/s", "ctas": ctas.value, "segments": segs.value,
+            "max_abs_diff_vs_engine": float((ref_out.float() - layer.out.float()).abs().max().item())}
+
+
+def c5_heads(torch, pa, dist, world, rank, stream, measure, max_over_ranks, args):
+    """BASELINE config 5: Hq 64 / Hkv 8, batch 256 x 16384, e4m3, 16-token pages, kv heads sharded over the ranks
+    (one fixed problem: strong scaling), outputs gathered by the decode kernel's peer stores."""
+    dtype, B, L, hq, hkv, page, desc = WORKLOADS["c5"]
+    if args.c5_batch:
+        B = args.c5_batch
+    l_hq, l_hkv = hq // world, hkv // world
+    layer = Layer(torch, pa, dtype, B, L, l_hq, l_hkv, page, 4321 + rank, stream, shared_source=True)
+    gather = Gather(torch, pa, dist, layer, "heads", args.gather, world, rank) if world > 1 else None
+    m = measure(layer, gather, args.steps, args.warmup)
+    check = gather.check() if gather is not None else None
+    launch = layer.launch()
+    full_bytes = algorithmic_bytes(dtype, [L] * B, hq, hkv, page)
+    local_bytes = layer.bytes
+    if gather is not None:
+        gather.close()
+    layer.close()
+    del layer
+    torch.cuda.empty_cache()
+    single = None
+    if world > 1:
+        # the unsharded layer on one GPU (rank 0), for the strong-scaling ratio; the others wait
+        if rank == 0:
+            full = Layer(torch, pa, dtype, B, L, hq, hkv, page, 4321, stream, shared_source=True)
+            single = measure_single(torch, pa, full, stream, args)
+            full.close()
+        dist.barrier()
+    else:
+        single = m["per_step"]
+    out = {"workload": desc if not args.c5_batch else desc + " [batch reduced to %d]" % B, "n_gpus": world,
+           "us_per_layer": m["per_step"] * 1e3, "us_per_layer_strict": m["per_strict"] * 1e3,
+           "us_decode_kernel_alone": m["per_kernel"] * 1e3,
+           "value": full_bytes / (m["per_step"] * 1e-3) / 1e9, "unit": "GB/s (whole layer, all GPUs)",
+           "per_gpu_gbs": local_bytes / (m["per_step"] * 1e-3) / 1e9, "scaling": "strong",
+           "kv_heads_per_gpu": l_hkv, "q_heads_per_gpu": l_hq, "launch": launch, "gather_check": check}
+    if rank == 0 and single is not None:
+        out["us_per_layer_one_gpu"] = single * 1e3
+        out["speedup_vs_one_gpu"] = single / m["per_step"]
+        out["strong_scaling_efficiency"] = single / m["per_step"] / world
+    return out
+
+
+def measure_single(torch, pa, layer, stream, args):
+    """Rank 0 alone: the same protocol without the rendezvous (no collective may be called by one rank)."""
+    flush_buf = torch.zeros(512 << 20, dtype=torch.uint8, device="cuda")
+    untimed = max(max(args.warmup, 3), 24 if pa.adaptive_cut() else 0)
+    for _ in range(untimed):
+        layer.replan()
+        pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)
+        layer.decode()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for s, e in ev:
+        pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)
+        s.record()
+        layer.decode()
+        e.record()
+    torch.cuda.synchronize()
+    return sum(s.elapsed_time(e) for s, e in ev) / len(ev)
 
 
 def main():
@@ -502,9 +824,11 @@ def main():
     ap.add_argument("--shard", default=None, choices=["batch", "heads"])
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--ctas", type=int, default=0)
-    ap.add_argument("--variant", type=int, default=None)
     ap.add_argument("--contiguous-pages", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--no-c5", action="store_true", help="skip the kv-head-sharded 70B-shaped layer after the headline")
+    ap.add_argument("--c5-batch", type=int, default=0, help="batch of that layer (default: the workload's 256)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

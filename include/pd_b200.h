@@ -100,13 +100,7 @@ int pd_tile_tokens(int dtype, int head_dim, int group, int* out);
 int pd_wave_ctas(int dtype, int head_dim, int group, int* out);
 int pd_default_ctas(int dtype, int head_dim, int group, int* out);
 
-/* Tuning knob with no counterpart in the reference, whose launch shape is a
- * compile-time constant (src/decode/decode.cu:14): selects one of the compiled CTA
- * shapes / pipeline depths (0 = default).  Also read once from the environment
- * variable PD_B200_VARIANT.  Changes pd_tile_tokens, so re-plan afterwards. */
-int pd_set_kernel_variant(int variant);
-int pd_kernel_variant(void);
-/* Second tuning knob, also without a counterpart in the reference.  fp16 layers with exactly 8 kv heads
+/* Tuning knob without a counterpart in the reference.  fp16 layers with exactly 8 kv heads
  * whose plan came from pd_make_plan (directly or through the cache) normally run the "head-fused"
  * schedule: the device plan also carries the step cut by rows, a tile is 16 tokens of all 8 kv heads
  * (one 32 KB box per page and pool for fp16 instead of eight 4 KB boxes fetched by different CTAs at
@@ -119,7 +113,7 @@ int pd_kernel_variant(void);
  * decode call. */
 int pd_set_head_fused(int mode);
 int pd_head_fused(void);
-/* Third knob without a counterpart in the reference: the adaptive cut.  SMs of one GPU do not stream at
+/* Second knob without a counterpart in the reference: the adaptive cut.  SMs of one GPU do not stream at
  * the same rate, and CTA c of a grid always runs on the same SM, so with the planner's equal shares the
  * slower SMs finish tens of microseconds after the others.  While this is on (default; environment
  * PD_B200_NO_ADAPTIVE=1 switches it off) every decode launch leaves (busy time, tiles) per CTA in a host
@@ -179,6 +173,12 @@ int  pd_device_plan_create(pd_device_plan** out);
 void pd_device_plan_destroy(pd_device_plan* dp);
 int  pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, int head_dim, void* stream);
 int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
+/* No counterpart in the reference, whose kernels have no bounded waits.  After pd_kernel_status has reported
+ * PD_KERNEL_TIMEOUT, the CTA that gave up has skipped its arrivals, so the arrival counters of the in-kernel
+ * merge inside this device plan may hold partial counts; a later launch of the same plan would merge rows too
+ * early or never.  This call clears them (stream-ordered memsets); the next pd_device_plan_upload / _build
+ * does so too.  Gathered outputs: see pd_gather_reset. */
+int  pd_device_plan_reset(pd_device_plan* dp, void* stream);
 
 /* Device-side planner.  No counterpart in the reference, whose plan is always cut on the host from host
  * lengths (src/decode/decode.cu:65-108) and copied over (decode.cu:112-156); its README lists a
@@ -221,6 +221,14 @@ int pd_paged_decode_bounded(int dtype, const pd_params* p, int num_pages, void* 
 int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const float* d_k_scales,
                            const float* d_v_scales, void* stream);
 
+/* What a decode of these params would launch (no counterpart in the reference, which has one kernel shape):
+ * out[0] schedule (0 the caller's plan as bound, 1 the same step cut by rows for the head-fused kernel,
+ * 2 the caller's plan cut in unequal shares by the adaptive cut), out[1] grid, out[2] tokens per tile,
+ * out[3] kv heads per tile, out[4] consumer warps per CTA, out[5] pipeline stages, out[6] CTAs per SM the
+ * shape is made for, out[7] needs_merge of that schedule (0 none, 1 merge kernel, 2 merged inside the decode
+ * kernel, 3 per row).  Pure host lookup; launches nothing. */
+int pd_describe_launch(int dtype, const pd_params* p, int* out);
+
 /* No counterpart in the reference (its DevicePlan always allocates, src/decode/decode.cu:131-141).
  * The same decode + merge as pd_paged_decode_bounded, for callers that cannot allow a device
  * allocation: a server that has already given all free HBM to its KV pool, so that a workspace
@@ -229,9 +237,13 @@ int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const f
  * cudaFree or other allocating call.
  *   - p->partial_out / p->partial_lse are ignored: the workspace for rows split across CTAs is
  *     an 8 MiB array built into the library (each GPU that loads the library carries it until
- *     the process exits).  num_segments is the plan's segment count; a plan that needs more than
- *     8 MiB, i.e. num_segments * group * (head_dim + 1) * 4 bytes, is refused with
- *     PD_INVALID_ARGUMENT and nothing is launched.  Headline shapes need 0.4 - 1.6 MiB.
+ *     the process exits).  num_segments is the plan's segment count (pd_plan_num_segments); a plan
+ *     that needs more than 8 MiB, i.e. num_segments * group * (head_dim + 1) * 4 bytes, is refused
+ *     with PD_INVALID_ARGUMENT and nothing is launched.  Headline shapes need 0.4 - 1.6 MiB.
+ *     The count is also checked on the device against the plan the kernels walk: if the bound plan
+ *     has more segments than declared (a count left over from an earlier plan, say), the CTAs whose
+ *     segments lie beyond it store nothing, the status word receives code 6 and the rows of those
+ *     CTAs stay unwritten; nothing is ever stored outside the array.
  *   - d_status: device word the kernel writes if a bounded wait expires; the caller zeroes it and
  *     reads it back when it wants to know.  NULL selects a built-in word that nothing reads.
  *   - The first call on each device looks up the built-in arrays' device addresses
@@ -251,12 +263,16 @@ int pd_kernel_status(void* stream, unsigned* status);
 
 /* Multi-GPU (no counterpart in the reference, which is single-GPU): the decode layer sharded over
  * the GPUs of one node, one process per GPU, with the output all-gather done by the decode
- * kernel itself.  Every rank owns a gathered-output buffer; the kernel's epilogue (and its
- * in-kernel merge) stores each output row into that buffer on EVERY peer with plain peer stores
- * over NVLink, and the last CTA raises a per-rank flag on every peer, then waits (bounded, ~1 s,
- * then PD_KERNEL_TIMEOUT via pd_kernel_status) until all peers' flags of the current step have
- * arrived.  No collective library call is involved.
- *   pd_gather_create   allocates this rank's block (two alternating output buffers + flags)
+ * kernel itself.  Every rank owns gathered-output buffers; the kernel's epilogue (and its
+ * in-kernel merge) stores each output row into the step's buffer on EVERY peer with plain 16-byte
+ * peer stores over NVLink, and the last CTA raises a per-rank flag on every peer.  pd_gather_wait
+ * then enqueues a one-warp kernel that waits (bounded, ~1 s, then PD_KERNEL_TIMEOUT via
+ * pd_kernel_status) until all peers' flags of the step have arrived.  No collective library call is
+ * involved.  Four buffers are used in rotation (step e fills buffer e mod 4), so a caller may launch
+ * step e+1's decode before it waits for step e: the wait then overlaps the next decode, and a step no
+ * longer ends with the slowest rank.  Rule for such callers: wait for step e (pd_gather_wait_epoch) and
+ * finish reading its buffer before launching step e+2.
+ *   pd_gather_create   allocates this rank's block (four output buffers in rotation + flags)
  *   pd_gather_export   writes the block's CUDA IPC handle (pd_gather_handle_bytes() bytes)
  *   pd_gather_connect  takes all ranks' handles, rank-major, and maps the peers' blocks
  *   pd_paged_decode_gather  pd_paged_decode_bounded with gathered output: this rank's
@@ -264,7 +280,9 @@ int pd_kernel_status(void* stream, unsigned* status);
  *       `row_stride_heads` heads (kv-head sharding: offset = rank * local heads; batch sharding:
  *       row_offset = first global row).  p->out is ignored.  Plans with split rows must be
  *       bound by pd_device_plan_bind (in-kernel merge).
- *   pd_gather_buffer   the local gathered buffer of step parity `which` (0/1; -1 = last step) */
+ *   pd_gather_buffer   the local gathered buffer number `which` (0..3: step mod 4; -1 = last step)
+ *   pd_gather_reset    after a PD_KERNEL_TIMEOUT: clears the grid's arrival counter, which a CTA that
+ *                      gave up has left short (see pd_device_plan_reset) */
 typedef struct pd_gather_group pd_gather_group;
 int      pd_gather_create(int world, int rank, size_t out_bytes, pd_gather_group** out);
 void     pd_gather_destroy(pd_gather_group* g);
@@ -276,15 +294,17 @@ unsigned pd_gather_epoch(const pd_gather_group* g);
 int      pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g,
                                 int row_stride_heads, int head_offset, int row_offset, void* stream);
 int      pd_gather_wait(pd_gather_group* g, void* stream);
+int      pd_gather_reset(pd_gather_group* g, void* stream);
 /* The same wait for a step the caller names (steps are numbered 1, 2, ... by pd_gather_epoch): lets a
  * pipelined caller wait for step k's rows while step k+1 is already in flight.  Waiting for a step
  * that no peer ever signals ends after the bounded ~1 s with PD_KERNEL_TIMEOUT in pd_kernel_status;
  * the context stays usable. */
 int      pd_gather_wait_epoch(pd_gather_group* g, unsigned epoch, void* stream);
-/* By default the decode kernel's last CTA itself waits (bounded) for all peers' flags before the
- * kernel ends, and pd_gather_wait has nothing left to do; with `on` = 0 the kernel only signals
- * and pd_gather_wait enqueues the separate one-warp wait kernel (for callers that want other
- * work between the decode and the point where the gathered rows are needed). */
+/* By default the decode kernel only signals and pd_gather_wait enqueues the separate one-warp wait
+ * kernel, so other work (the next step's decode) can sit between the decode and the point where the
+ * gathered rows are needed.  With `on` = 1 the decode kernel's last CTA itself waits (bounded) for all
+ * peers' flags before the kernel ends and pd_gather_wait has nothing left to do; the step then ends
+ * with the slowest rank. */
 int      pd_gather_set_wait_in_kernel(pd_gather_group* g, int on);
 
 /* read_kernel of the reference's benchmark (bench/bench_decode.cu:69-78, "copy" mode
@@ -338,6 +358,8 @@ int    pd_cache_plan_device(pd_cache* c, const int* d_slot_ids, int batch, int n
 int    pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream);
 int    pd_cache_decode(pd_cache* c, const void* d_q, void* d_out, int batch, int num_q_heads,
                        int num_ctas, void* stream);
+/* pd_describe_launch for the cache's current plan: what the next run() launches.  No counterpart in the reference. */
+int    pd_cache_describe_launch(const pd_cache* c, int* out);
 const pd_plan* pd_cache_last_plan(const pd_cache* c);  /* borrowed; valid until the next plan */
 int    pd_cache_params(const pd_cache* c, pd_params* out);
 int    pd_cache_seq_len(const pd_cache* c, int slot);

@@ -6,7 +6,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libpd_b200.so")
+LIB_PATH = os.environ.get("PD_B200_LIB") or os.path.join(HERE, "libpd_b200.so")   # PD_B200_LIB: a tuning build elsewhere
 
 PD_OK, PD_INVALID_ARGUMENT, PD_LENGTH_ERROR, PD_CUDA_ERROR, PD_OUT_OF_PAGES, PD_KERNEL_TIMEOUT, PD_INTERNAL = range(7)
 
@@ -61,8 +61,6 @@ SIGNATURES = {
     "pd_tile_tokens": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p]),
     "pd_wave_ctas": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p]),
     "pd_default_ctas": (C.c_int, [C.c_int, C.c_int, C.c_int, _i32p]),
-    "pd_set_kernel_variant": (C.c_int, [C.c_int]),
-    "pd_kernel_variant": (C.c_int, []),
     "pd_set_adaptive_cut": (C.c_int, [C.c_int]),
     "pd_adaptive_cut": (C.c_int, []),
     "pd_adaptive_cut_reset": (C.c_int, []),
@@ -86,6 +84,8 @@ SIGNATURES = {
     "pd_device_plan_destroy": (None, [_vp]),
     "pd_device_plan_upload": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp]),
     "pd_device_plan_bind": (C.c_int, [_vp, C.POINTER(pd_params)]),
+    "pd_device_plan_reset": (C.c_int, [_vp, _vp]),
+    "pd_describe_launch": (C.c_int, [C.c_int, C.POINTER(pd_params), _i32p]),
     "pd_device_plan_build": (C.c_int, [_vp, C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_device_plan_info": (C.c_int, [_vp, _i32p, _vp]),
     "pd_device_plan_fetch": (C.c_int, [_vp, C.POINTER(_vp), _vp]),
@@ -102,6 +102,7 @@ SIGNATURES = {
     "pd_gather_epoch": (C.c_uint, [_vp]),
     "pd_paged_decode_gather": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_gather_wait": (C.c_int, [_vp, _vp]),
+    "pd_gather_reset": (C.c_int, [_vp, _vp]),
     "pd_gather_wait_epoch": (C.c_int, [_vp, C.c_uint, _vp]),
     "pd_gather_set_wait_in_kernel": (C.c_int, [_vp, C.c_int]),
     "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
@@ -124,6 +125,7 @@ SIGNATURES = {
     "pd_cache_plan_device": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_cache_run": (C.c_int, [_vp, _vp, _vp, _vp]),
     "pd_cache_decode": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "pd_cache_describe_launch": (C.c_int, [_vp, _i32p]),
     "pd_cache_last_plan": (_vp, [_vp]),
     "pd_cache_params": (C.c_int, [_vp, C.POINTER(pd_params)]),
     "pd_cache_seq_len": (C.c_int, [_vp, C.c_int]),

@@ -4,6 +4,10 @@
 
 The library is the product: there is no fallback path, importing the package
 without it raises.
+
+Tuning builds: extra nvcc flags come from the environment variable PD_B200_NVCC_FLAGS
+(e.g. -DPD_B200_FP8_CONFIG=4,2,2,3 for another CTA shape of the e4m3 kernel) and
+`-o PATH` writes the library somewhere else; PD_B200_LIB points the package at it.
 """
 import os
 import subprocess
@@ -36,18 +40,19 @@ def stale():
     return any(os.path.getmtime(d) > t for d in DEPS)
 
 
-def build(force=False, verbose=False):
-    if not force and not stale():
+def build(force=False, verbose=False, out=None):
+    if not force and not out and not stale():
         return LIB
-    cmd = [nvcc()] + NVCC_FLAGS + ["-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", LIB] + SOURCES
+    extra = os.environ.get("PD_B200_NVCC_FLAGS", "").split()
+    cmd = [nvcc()] + NVCC_FLAGS + extra + ["-I" + os.path.join(ROOT, "include"), "-I" + CSRC, "-o", out or LIB] + SOURCES
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
         print(" ".join(cmd))
     subprocess.check_call(cmd)
-    return LIB
+    return out or LIB
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print(LIB)
+    target = sys.argv[sys.argv.index("-o") + 1] if "-o" in sys.argv else None
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, out=target))

@@ -1,7 +1,10 @@
-"""Optional comparison with FlashInfer's paged decode on the same tensors, in the spirit of the
-reference's scripts/compare_flashinfer.py (its published claim is "within a few percent of FlashInfer").
-FlashInfer is never a dependency of the engine: if it is not importable (or cannot build its kernels
-here) the script says so and exits 0.
+"""Optional comparison with FlashInfer's paged decode on the same tensors (the reference's published claim
+is "within a few percent of FlashInfer").  To be comparable with the reference's own harness the inputs
+and the fp32 check restate scripts/compare_flashinfer.py:80-126 of the reference: `make_inputs` builds the
+same HND pools, per-tensor scales amax/448 and permuted page table (:80-97), `fp32_reference` is the same
+per-row einsum softmax (:113-126), and FlashInfer is driven through the same wrapper call.  The timing loop,
+the CSV and the command line are this package's.  FlashInfer is never a dependency of the engine: if it is
+not importable (or cannot build its kernels here) the script says so and exits 0.
 
     python -m paged_attention_b200.compare_flashinfer [--iters 30] [--shapes 32x8192,64x8192,128x4096]
 
@@ -60,7 +63,7 @@ def main(argv=None):
     stream = torch.cuda.current_stream().cuda_stream
 
     def time_cold(fn, before=None):
-        for _ in range(24 if before else 5):
+        for _ in range(24):          # the same warm-up for both sides (the engine's adaptive cut settles within it)
             if before:
                 before()
             pa.stream_read(flush_buf, flush_buf.numel(), 148 * 8, stream)

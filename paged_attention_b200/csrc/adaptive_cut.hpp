@@ -77,10 +77,17 @@ RateTable* rate_table(const void* fn, int grid, bool create = true) {
 }
 
 // Folds the latest record into the weights.  Only records of launches long enough that the fixed cost of
-// a CTA (a few microseconds) does not matter are used.
-void update_weights(RateTable* t, cudaStream_t stream) {
-    if (!t) return;
+// a CTA (a few microseconds) does not matter are used.  Returns a copy of the weights taken under the lock
+// (empty while there are none): another host thread planning for the same (device, kernel, grid) may
+// rewrite the table's own vector at any time.
+void fold_readings(RateTable* t, cudaStream_t stream);
+std::vector<float> update_weights(RateTable* t, cudaStream_t stream) {
+    if (!t) return {};
     std::lock_guard<std::mutex> lock(g_rate_mutex);
+    fold_readings(t, stream);
+    return t->weights;
+}
+void fold_readings(RateTable* t, cudaStream_t stream) {
     // Use the copy queued by an earlier upload if it has landed, then queue the next one behind the
     // launches issued so far.  Nothing here waits for the device.
     const bool have_copy = t->copy_queued && cudaEventQuery(t->copied) == cudaSuccess;

@@ -45,10 +45,6 @@ namespace pdk {
 constexpr int HEAD_DIM = 128;
 constexpr int OSTRIDE  = HEAD_DIM + 4;   // padded row of the cross-warp merge scratch (floats)
 
-// diagnostic flags carried above the box-size bits of the kernel's btl_flags argument
-constexpr int FLAG_LOAD_ONLY = 0x100;
-constexpr int FLAG_NO_L2_HINT = 0x200;
-
 // pd_params::needs_merge: 0 = no row is split, 1 = run merge_segments_kernel after the decode
 // kernel (any workspace of [segments][group][129] floats will do), 2 = the decode kernel merges
 // itself; the workspace then carries one zeroed int per (row, kv head) after the LSE array.
@@ -66,6 +62,7 @@ constexpr unsigned ST_EMPTY_TIMEOUT = 2;   // producer gave up waiting for a fre
 constexpr unsigned ST_DRAIN_TIMEOUT = 3;   // producer gave up draining copies after an abort
 constexpr unsigned ST_SYNC_TIMEOUT  = 4;   // a consumer warp gave up waiting for its siblings
 constexpr unsigned ST_GATHER_TIMEOUT = 5;  // a peer's "slice has landed" flag never arrived
+constexpr unsigned ST_WORKSPACE      = 6;  // the plan has more segments than the split-row workspace was sized for
 
 // Where outputs go.  world == 0: to pd_params::out, [batch][num_q_heads][128].  world > 0: this
 // GPU's rows are one slice of a layout gathered over `world` GPUs of the node, and every output
@@ -156,8 +153,12 @@ struct Shape {
     // their own rows from global memory at a segment's start instead.)
     static constexpr int Q_SLOT_BYTES = HEADS > 1 ? 0 : GROUP * HEAD_DIM * 2;
     static constexpr int Q_BYTES      = C::STAGES * Q_SLOT_BYTES;
+    // Head-fused: [GROUP][128] fp16 staging rows per consumer warp, from which finished rows leave as 16-byte stores.
+    static constexpr int OUT_STAGE_OFFSET = PIPE_BYTES + Q_BYTES + MERGE_BYTES + ((BAR_BYTES + 15) & ~15);
+    static constexpr int OUT_STAGE_BYTES  = HEADS > 1 ? C::WARPS * GROUP * HEAD_DIM * 2 : 0;
     // +1024: the pipeline is aligned to the 128B-swizzle period by hand
-    static constexpr int SMEM_BYTES  = 1024 + PIPE_BYTES + Q_BYTES + MERGE_BYTES + BAR_BYTES;
+    static constexpr int SMEM_BYTES  = 1024 + OUT_STAGE_OFFSET + OUT_STAGE_BYTES;
+    static_assert(sizeof(KV) == 2 || (HEADS == 1 && C::GROUPS_PER_WARP % 2 == 0), "e4m3 cache: a warp works on 32-token units");
     static_assert(GROUP >= 1 && GROUP <= 8, "a KV group fills the 8 columns of one MMA");
 };
 
@@ -211,18 +212,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
                  " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(pol) : "memory");
-}
-__device__ __forceinline__ void tma_load_4d_nohint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                                   int c0, int c1, int c2, int c3) {
-    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_5d_nohint(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                                   int c0, int c1, int c2, int c3, int c4) {
-    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
-                 " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-                 :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
 // Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -292,30 +281,29 @@ __device__ __forceinline__ uint32_t swz(uint32_t row_off, int c) {
     return row_off + (((c ^ (row_off >> 7)) & 7) << 4);
 }
 
-// ---- one 16-token group: S^T = K Q^T, online softmax, O^T += V^T P^T ------------------------------
+// ---- fp16 cache, one 16-token group: S^T = K Q^T, online softmax, O^T += V^T P^T -------------------
 //
 // `rows(t, panel)` gives the byte offset, from the tile base, of the 128-byte shared-memory row
-// that holds token t of the group's (row, kv head), panel = dims 64*panel.. (fp16) or 0 (fp8).
+// that holds token t of the group's (row, kv head), panel = dims 64*panel...
 // grp_row is the first token of the group inside the tile; grp_valid (1..16+) how many of its tokens exist.
 // Returns true if it wrote to shared memory (dead V rows cleared), so the caller fences before
 // handing the stage back to the copy engine.
-template<typename KV, typename Rows>
-__device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint32_t v_tile, const Rows rows,
-                                              const int grp_row, const int grp_valid, const uint32_t (&qb)[8][2],
-                                              float (&acc)[8][4], float (&m_run)[2], float (&l_run)[2],
-                                              const float qk_scale, const int lane)
+template<typename Rows>
+__device__ __forceinline__ bool process_group_f16(const uint32_t k_tile, const uint32_t v_tile, const Rows rows,
+                                                  const int grp_row, const int grp_valid, const uint32_t (&qb)[8][2],
+                                                  float (&acc)[8][4], float (&m_run)[2], float (&l_run)[2],
+                                                  const float qk_scale, const int lane)
 {
-    constexpr bool FP8 = sizeof(KV) == 1;
-    const int g = lane >> 2, qd = lane & 3;
+    const int g = lane >> 2;
     bool wrote = false;
     if (grp_valid < 16) {
         // Rows past the end hold whatever the page or the stage held before; a NaN
         // there would survive P = 0 in the PV product, so clear V's dead rows.
-        constexpr int CH = HEAD_DIM * static_cast<int>(sizeof(KV)) / 16;
+        constexpr int CH = HEAD_DIM * 2 / 16;
         for (int idx = lane; idx < 16 * CH; idx += 32) {
             const int r = idx / CH, c = idx % CH;
             if (r >= grp_valid)
-                sts128_zero(v_tile + rows(grp_row + r, FP8 ? 0 : (c >> 3)) + ((c & 7) << 4));
+                sts128_zero(v_tile + rows(grp_row + r, c >> 3) + ((c & 7) << 4));
         }
         wrote = true;
         __syncwarp();
@@ -323,7 +311,7 @@ __device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint3
 
     // ---- 1. S^T = K Q^T : 16 tokens x 8 heads, two interleaved accumulators.
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-    if constexpr (!FP8) {
+    {
         const int t = grp_row + (lane & 7) + ((lane >> 3) & 1) * 8;
         const uint32_t r0 = rows(t, 0), r1 = rows(t, 1);
         const int hi = lane >> 4;
@@ -333,22 +321,6 @@ __device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint3
             ldmatrix_x4(a, k_tile + swz(ks < 4 ? r0 : r1, (ks & 3) * 2 + hi));
             if (ks & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
             else        mma_16816(s0, a, qb[ks][0], qb[ks][1]);
-        }
-    } else {
-        const uint32_t r0 = rows(grp_row + g, 0), r1 = rows(grp_row + g + 8, 0);
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const uint4 lo = lds128(k_tile + swz(r0, 2 * qd + j));
-            const uint4 hi = lds128(k_tile + swz(r1, 2 * qd + j));
-            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-            for (int m = 0; m < 4; m++) {
-                const uint32_t a[4] = {fp8x2_to_half2(wl[m] & 0xffffu), fp8x2_to_half2(wh[m] & 0xffffu),
-                                       fp8x2_to_half2(wl[m] >> 16),     fp8x2_to_half2(wh[m] >> 16)};
-                const int ks = 4 * j + m;
-                if (m & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
-                else       mma_16816(s0, a, qb[ks][0], qb[ks][1]);
-            }
         }
     }
 
@@ -387,7 +359,7 @@ __device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint3
     // ---- 3. O^T += V^T P^T.  P^T's B fragment = transposed 8x8 blocks of the scores.
     const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));   // tokens 0..7
     const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));   // tokens 8..15
-    if constexpr (!FP8) {
+    {
         const int t = grp_row + (lane & 7) + ((lane >> 4) & 1) * 8;
         const uint32_t r0 = rows(t, 0), r1 = rows(t, 1);
         const int hi = (lane >> 3) & 1;
@@ -397,29 +369,220 @@ __device__ __forceinline__ bool process_group(const uint32_t k_tile, const uint3
             ldmatrix_x4_trans(a, v_tile + swz(mt < 4 ? r0 : r1, (mt & 3) * 2 + hi));
             mma_16816(acc[mt], a, pb0, pb1);
         }
-    } else {
-        // This lane: tokens 2qd, 2qd+1, 2qd+8, 2qd+9, dims 16g..16g+15.  M-tile mt has
-        // row g = dim 16g + 2mt and row g+8 = dim 16g + 2mt + 1.
-        uint32_t vw[4][4];
+    }
+    return wrote;
+}
+
+// ---- e4m3 cache, one 32-token group ------------------------------------------------------------------
+//
+// The cache bytes go to the tensor cores as they are (mma.m16n8k32 on e4m3 operands): nothing is widened
+// in registers.  What meets them has to be e4m3 too, so the fp16 query rows are split, exactly, into three
+// e4m3 terms (q * 2^e = q1 + q2 + q3 with a per-head power of two that brings the row's largest element
+// just under 256; each term takes the next four significant bits, eleven in all), and the softmax weights,
+// which the fp16 path rounds to fp16 before the PV product, are rounded to fp16 likewise and then split the
+// same way (256 p = p1 + p2 + p3).  Three MMAs per operand tile instead of one, no conversion per cache byte:
+// 48 tensor and about 100 other instructions per 32 tokens, against about 660 with the bytes widened to
+// fp16 first, which had made the fp8 layer issue-bound.
+//
+// Fragment bookkeeping.  K tile as the A operand (tokens x 32 dims per k-step): lane (g, qd) reads the 16-byte
+// chunks 2qd and 2qd+1 of its two token rows; word ks of chunk 2qd is a0/a1 of k-step ks (dims 32qd + 4ks + j),
+// word ks of chunk 2qd+1 is a2/a3 (dims 32qd + 16 + 4ks + j); the query fragments use the same dims.
+// MMA row r of a 16-token half holds token tau(r) = r (r < 8), 8 + ((r + 4) & 7) (r >= 8): any assignment
+// would do for QK, this one makes the 16 rows that one transposed 8-bit ldmatrix of V touches fall into
+// different bank groups under the 128-byte swizzle.  V tile as the A operand of O^T += V^T P^T (16 dims x 32
+// tokens): ldmatrix.m16n16.x2.trans.b8 over the 16-byte chunk `mt` of 32 token rows yields a0..a3 directly;
+// matrix row k of a half is token tau(2(k >> 2) + (k >> 1 & 1) + 8(k & 1)), which is where movmatrix puts the
+// weight of that token in P^T's B fragment (bytes paired as (row r, row r + 8) per head before the transpose).
+//
+// m_run carries the running maximum minus 8, so that the weights are 256 exp2(x - max): up to 256 instead
+// of 1, which keeps three e4m3 terms of small weights out of the subnormal range.  l_run, the accumulators
+// and the LSE m_run + log2(l_run) are then those of a softmax taken relative to (max - 8): the same
+// quantities every later step (cross-warp combine, partials, merge) expects.
+__device__ __forceinline__ int tau16(int r) { return r < 8 ? r : 8 + ((r + 4) & 7); }
+
+// Four floats -> the four nearest e4m3 bytes (byte j from v[j]); v is left holding the residuals.
+__device__ __forceinline__ uint32_t split_e4m3x4(float (&v)[4]) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(v[1]), "f"(v[0]));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(v[3]), "f"(v[2]));
+    uint32_t blo, bhi;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(blo) : "h"(lo));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(bhi) : "h"(hi));
+    const float2 flo = __half22float2(*reinterpret_cast<const __half2*>(&blo));
+    const float2 fhi = __half22float2(*reinterpret_cast<const __half2*>(&bhi));
+    v[0] -= flo.x; v[1] -= flo.y; v[2] -= fhi.x; v[3] -= fhi.y;
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+// half2 -> two e4m3 bytes (low half -> low byte); h is left holding the residual (exact in fp16).
+__device__ __forceinline__ uint32_t split_e4m3x2(uint32_t& h) {
+    uint16_t e;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(e) : "r"(h));
+    uint32_t back;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(back) : "h"(e));
+    asm("sub.rn.f16x2 %0, %0, %1;" : "+r"(h) : "r"(back));
+    return e;
+}
+__device__ __forceinline__ uint32_t to_e4m3x2(uint32_t h) {
+    uint16_t e;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(e) : "r"(h));
+    return e;
+}
+// D(16x8) += A(16x32, row) * B(32x8, col), e4m3 in, fp32 accumulate.
+__device__ __forceinline__ void mma_16832_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// 16 dims x 32 tokens of a byte tile, transposed into the A fragment of mma.m16n8k32: lanes 0..15 give the
+// addresses of the 16-byte chunks of matrix rows (tokens) 0..15, lanes 16..31 of rows 16..31.
+__device__ __forceinline__ void ldmatrix_b8_x2_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// The query row of head g (fp16, 128 dims at `qrow` in shared memory) as three sets of B fragments:
+// qb[4 * term + ks] for k-step ks.  Returns e with q * 2^e split; dead rows (live = false) give zeros.
+__device__ __forceinline__ int load_q_e4m3(uint32_t (&qb)[12][2], const uint32_t qrow, const bool live, const int lane)
+{
+    const int qd = lane & 3;
+    uint32_t raw[16];                          // dims 32qd .. 32qd+31 of this head, two per word
 #pragma unroll
-        for (int r = 0; r < 4; r++) {
-            const int t = grp_row + 2 * qd + (r & 1) + (r >> 1) * 8;
-            const uint4 v = lds128(v_tile + swz(rows(t, 0), g));
-            vw[r][0] = v.x; vw[r][1] = v.y; vw[r][2] = v.z; vw[r][3] = v.w;
+    for (int c = 0; c < 4; c++) {
+        const uint4 w = lds128(qrow + (32 * qd + 8 * c) * 2);
+        raw[4 * c] = live ? w.x : 0u; raw[4 * c + 1] = live ? w.y : 0u;
+        raw[4 * c + 2] = live ? w.z : 0u; raw[4 * c + 3] = live ? w.w : 0u;
+    }
+    __half2 mx2 = __float2half2_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < 16; i++) mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __half2*>(&raw[i])));
+    float mx = fmaxf(__low2float(mx2), __high2float(mx2));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    // mx in [2^(E-127), 2^(E-126)): scaled by 2^(134-E) it lies in [128, 256)
+    const int E = static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu);
+    const int e = (E >= 8 && E < 255) ? 134 - E : 0;
+    const float up = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {          // b0: dims 4ks.., b1: dims 16 + 4ks.. (of the lane's 32)
+            const int w = 8 * half + 2 * ks;
+            const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw[w]));
+            const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw[w + 1]));
+            float v[4] = {f01.x * up, f01.y * up, f23.x * up, f23.y * up};
+            qb[ks][half]     = split_e4m3x4(v);
+            qb[4 + ks][half] = split_e4m3x4(v);
+            qb[8 + ks][half] = split_e4m3x4(v);
         }
+    }
+    return e;
+}
+
+// grp_row: first token of the group inside the tile; grp_valid (1..32+): how many of its tokens exist.
+// col_scale: softmax scale (base 2, with the K scale and 2^-e of the query split) of heads 2qd, 2qd+1.
+template<typename Rows>
+__device__ __forceinline__ bool process_group_e4m3(const uint32_t k_tile, const uint32_t v_tile, const Rows rows,
+                                                   const int grp_row, const int grp_valid, const uint32_t (&qb)[12][2],
+                                                   float (&acc)[8][4], float (&m_run)[2], float (&l_run)[2],
+                                                   const float (&col_scale)[2], const int lane)
+{
+    const int g = lane >> 2, qd = lane & 3;
+    bool wrote = false;
+    if (grp_valid < 32) {
+        // dead V rows: a NaN byte there would survive a zero weight in the PV product
+        for (int idx = lane; idx < 32 * 8; idx += 32) {
+            const int r = idx >> 3, c = idx & 7;
+            if (r >= grp_valid) sts128_zero(v_tile + rows(grp_row + r, 0) + (c << 4));
+        }
+        wrote = true;
+        __syncwarp();
+    }
+
+    // ---- 1. S^T = K Q^T for both 16-token halves; one accumulator per query term.
+    const int tok_lo = g, tok_hi = tau16(g + 8);      // tokens of MMA rows g, g + 8 within a half
+    float x[2][4];
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
-            // bytes [t0 d, t1 d, t0 d+1, t1 d+1] for d = 4w (lo) and 4w+2 (hi)
-            const uint32_t lo01 = __byte_perm(vw[0][w], vw[1][w], 0x5140u);
-            const uint32_t hi01 = __byte_perm(vw[0][w], vw[1][w], 0x7362u);
-            const uint32_t lo23 = __byte_perm(vw[2][w], vw[3][w], 0x5140u);
-            const uint32_t hi23 = __byte_perm(vw[2][w], vw[3][w], 0x7362u);
-            const uint32_t a_lo[4] = {fp8x2_to_half2(lo01 & 0xffffu), fp8x2_to_half2(lo01 >> 16),
-                                      fp8x2_to_half2(lo23 & 0xffffu), fp8x2_to_half2(lo23 >> 16)};
-            const uint32_t a_hi[4] = {fp8x2_to_half2(hi01 & 0xffffu), fp8x2_to_half2(hi01 >> 16),
-                                      fp8x2_to_half2(hi23 & 0xffffu), fp8x2_to_half2(hi23 >> 16)};
-            mma_16816(acc[2 * w],     a_lo, pb0, pb1);
-            mma_16816(acc[2 * w + 1], a_hi, pb0, pb1);
+    for (int hh = 0; hh < 2; hh++) {
+        const uint32_t r0 = rows(grp_row + 16 * hh + tok_lo, 0), r1 = rows(grp_row + 16 * hh + tok_hi, 0);
+        const uint4 a02 = lds128(k_tile + swz(r0, 2 * qd)), a02b = lds128(k_tile + swz(r0, 2 * qd + 1));
+        const uint4 a13 = lds128(k_tile + swz(r1, 2 * qd)), a13b = lds128(k_tile + swz(r1, 2 * qd + 1));
+        const uint32_t w0[4] = {a02.x, a02.y, a02.z, a02.w}, w2[4] = {a02b.x, a02b.y, a02b.z, a02b.w};
+        const uint32_t w1[4] = {a13.x, a13.y, a13.z, a13.w}, w3[4] = {a13b.x, a13b.y, a13b.z, a13b.w};
+        float s[3][4];
+#pragma unroll
+        for (int t = 0; t < 3; t++) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+            for (int t = 0; t < 3; t++)
+                mma_16832_e4m3(s[t], w0[ks], w1[ks], w2[ks], w3[ks], qb[4 * t + ks][0], qb[4 * t + ks][1]);
+#pragma unroll
+        for (int i = 0; i < 4; i++) x[hh][i] = ((s[2][i] + s[1][i]) + s[0][i]) * col_scale[i & 1];
+        if (grp_valid < 32) {
+            if (16 * hh + tok_lo >= grp_valid) { x[hh][0] = -INFINITY; x[hh][1] = -INFINITY; }
+            if (16 * hh + tok_hi >= grp_valid) { x[hh][2] = -INFINITY; x[hh][3] = -INFINITY; }
+        }
+    }
+
+    // ---- 2. online softmax over the 32 tokens.  This lane: 4 tokens, heads 2qd, 2qd+1.
+    float mx[2] = {fmaxf(fmaxf(x[0][0], x[0][2]), fmaxf(x[1][0], x[1][2])),
+                   fmaxf(fmaxf(x[0][1], x[0][3]), fmaxf(x[1][1], x[1][3]))};
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+        mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float m_new = fmaxf(m_run[h], mx[h] - 8.f);
+        alpha[h] = exp2f(m_run[h] - m_new);
+        m_run[h] = m_new;
+    }
+    float pr[2][4];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) pr[hh][i] = exp2f(x[hh][i] - m_run[i & 1]);
+    l_run[0] = l_run[0] * alpha[0] + ((pr[0][0] + pr[0][2]) + (pr[1][0] + pr[1][2]));
+    l_run[1] = l_run[1] * alpha[1] + ((pr[0][1] + pr[0][3]) + (pr[1][1] + pr[1][3]));
+    // the accumulators only change scale when some maximum moved, which after the first tiles is rare
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+            acc[mt][0] *= alpha[0]; acc[mt][1] *= alpha[1];
+            acc[mt][2] *= alpha[0]; acc[mt][3] *= alpha[1];
+        }
+    }
+
+    // ---- 3. the weights as three e4m3 terms each, transposed into B fragments.
+    uint32_t pb[3][2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        uint32_t h02 = pack_half2(pr[hh][0], pr[hh][2]);     // head 2qd:   rows g, g + 8
+        uint32_t h13 = pack_half2(pr[hh][1], pr[hh][3]);     // head 2qd+1
+        const uint32_t t0 = split_e4m3x2(h02) | (split_e4m3x2(h13) << 16);
+        const uint32_t t1 = split_e4m3x2(h02) | (split_e4m3x2(h13) << 16);
+        const uint32_t t2 = to_e4m3x2(h02) | (to_e4m3x2(h13) << 16);
+        pb[0][hh] = movmatrix_trans(t0);
+        pb[1][hh] = movmatrix_trans(t1);
+        pb[2][hh] = movmatrix_trans(t2);
+    }
+
+    // ---- 4. O^T += V^T P^T.
+    {
+        const int k = lane & 15;
+        const int t = grp_row + 16 * (lane >> 4) + tau16(2 * (k >> 2) + ((k >> 1) & 1) + 8 * (k & 1));
+        const uint32_t r = rows(t, 0);
+#pragma unroll
+        for (int mt = 0; mt < 8; mt++) {
+            uint32_t a[4];
+            ldmatrix_b8_x2_trans(a, v_tile + swz(r, mt));
+            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[0][0], pb[0][1]);
+            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[1][0], pb[1][1]);
+            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[2][0], pb[2][1]);
         }
     }
     return wrote;
@@ -551,15 +714,18 @@ __device__ __forceinline__ void signal_peers(const GatherOut& gp, unsigned* stat
 template<typename KV, int GROUP, typename C>
 __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const int btl_flags /* log2(box tokens) | diagnostic flags */,
+                    const __grid_constant__ CUtensorMap v_map, const int btl /* log2(tokens per box) */,
+                    const int seg_limit /* segments the split-row workspace holds; 0 = sized by the plan's owner */,
                     unsigned* __restrict__ status, const __grid_constant__ GatherOut gp,
                     const __grid_constant__ HeadScales hs, const __grid_constant__ CtaStats st)
 {
     const unsigned long long t_entry = (st.slots && threadIdx.x == 0) ? global_ns() : 0ull;
-    const int  btl     = btl_flags & 0xff;
-    const bool no_math = (btl_flags & FLAG_LOAD_ONLY) != 0;   // diagnostic: stream the tiles, skip the arithmetic
-    // diagnostic: use fewer pipeline stages than were allocated (bits 12..15, 0 = all)
-    const int  nst     = ((btl_flags >> 12) & 0xf) ? min(C::STAGES, (btl_flags >> 12) & 0xf) : C::STAGES;
+#ifdef PD_B200_LOAD_ONLY
+    constexpr bool no_math = true;    // diagnostic build: stream the tiles, skip the arithmetic
+#else
+    constexpr bool no_math = false;
+#endif
+    constexpr int nst = C::STAGES;
     using S = Shape<KV, GROUP, C>;
     constexpr bool FP8 = sizeof(KV) == 1;
     constexpr int STAGES = C::STAGES;
@@ -584,6 +750,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     const int seg_end   = p.cta_seg_begin[blockIdx.x + 1];
     if (seg_begin >= seg_end) {
         if (gp.world && threadIdx.x == 0) signal_peers(gp, status);   // an idle CTA still counts towards "grid done"
+        return;
+    }
+    if (seg_limit > 0 && seg_end > seg_limit) {
+        // A workspace of fixed size (the built-in one) and a plan with more segments than the caller
+        // declared: this CTA's partial rows would land outside it.  Nothing is stored; the status word says so.
+        if (threadIdx.x == 0) atomicCAS(status, 0u, (ST_WORKSPACE << 24) | (blockIdx.x & 0xffffffu));
         return;
     }
 
@@ -648,15 +820,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const int head_coord = S::HEADS == 1 ? sg.y : 0;   // a head-fused box spans kv heads 0..7
             auto copy_box = [&](int j, int page) {
                 const int tok_in_page = (tile_tok + (j << btl)) % ps;
-                if (btl_flags & FLAG_NO_L2_HINT) {
-                    if constexpr (FP8) {
-                        tma_load_4d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, head_coord, page);
-                        tma_load_4d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, head_coord, page);
-                    } else {
-                        tma_load_5d_nohint(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page);
-                        tma_load_5d_nohint(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, 0, head_coord, page);
-                    }
-                } else if constexpr (FP8) {
+                if constexpr (FP8) {
                     tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, head_coord, page, pol);
                     tma_load_4d(v_dst + j * box_bytes, &v_map, full_bar(stage), 0, tok_in_page, head_coord, page, pol);
                 } else {
@@ -731,7 +895,8 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 
     float acc[8][4];
     float m_run[2], l_run[2];
-    uint32_t qb[8][2];          // Q^T B-fragments for the 8 k-steps
+    uint32_t qb[FP8 ? 12 : 8][2];   // Q^T B-fragments: fp16, 8 k-steps; e4m3, three terms of 4 k-steps
+    float col_scale[2] = {qk_scale, qk_scale};   // e4m3: qk_scale / 2^e of heads 2qd, 2qd+1 (e: the query split's exponent)
 
     unsigned tiles_done = 0;
     int c_stage = 0;            // stage of the next tile to consume and the parity of its round
@@ -763,17 +928,10 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 + (static_cast<size_t>(sg.x) * p.num_q_heads + warp * GROUP + (live ? g : 0)) * HEAD_DIM;
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-                if constexpr (FP8) {
-                    const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
-                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(qrow + db));
-                    qb[ks][0] = live ? v.x : 0u;
-                    qb[ks][1] = live ? v.y : 0u;
-                } else {
-                    const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd));
-                    const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd));
-                    qb[ks][0] = live ? lo : 0u;
-                    qb[ks][1] = live ? hi : 0u;
-                }
+                const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd));
+                const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd));
+                qb[ks][0] = live ? lo : 0u;
+                qb[ks][1] = live ? hi : 0u;
             }
         }
 #pragma unroll
@@ -790,15 +948,15 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 need_q = false;
                 const bool live = g < GROUP;
                 const uint32_t qrow = q_slots + stage * S::Q_SLOT_BYTES + (live ? g : 0) * (HEAD_DIM * 2);
+                if constexpr (FP8) {
+                    const int e = load_q_e4m3(qb, qrow, live, lane);
+                    // this lane's score columns are heads 2qd, 2qd+1, whose exponents live in lanes with g = 2qd, 2qd+1
+                    const int e0 = __shfl_sync(0xffffffffu, e, 8 * qd), e1 = __shfl_sync(0xffffffffu, e, 8 * qd + 4);
+                    col_scale[0] = qk_scale * __uint_as_float(static_cast<uint32_t>(127 - e0) << 23);
+                    col_scale[1] = qk_scale * __uint_as_float(static_cast<uint32_t>(127 - e1) << 23);
+                } else {
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    if constexpr (FP8) {
-                        // k-slots {2qd,2qd+1,2qd+8,2qd+9} of k-step ks are dims db..db+3 (one fp8 word of K)
-                        const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
-                        const uint2 v = lds64(qrow + db * 2);
-                        qb[ks][0] = live ? v.x : 0u;
-                        qb[ks][1] = live ? v.y : 0u;
-                    } else {
+                    for (int ks = 0; ks < 8; ks++) {
                         const uint32_t lo = lds32(qrow + (ks * 16 + 2 * qd) * 2);
                         const uint32_t hi = lds32(qrow + (ks * 16 + 8 + 2 * qd) * 2);
                         qb[ks][0] = live ? lo : 0u;
@@ -811,16 +969,19 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const int valid = sg.w - tok;   // tokens of this tile that exist (may exceed TILE)
             bool wrote = false;
 
+            // a warp's unit of work: 16 tokens (fp16 cache) or 32 tokens (e4m3 cache, one k-step of its MMA)
+            constexpr int UNIT = FP8 ? 2 : 1;
 #pragma unroll
-            for (int gi = 0; gi < C::GROUPS_PER_WARP; gi++) {
+            for (int gi = 0; gi < C::GROUPS_PER_WARP; gi += UNIT) {
                 const int grp_row = S::HEADS > 1 ? 0 : (warp * C::GROUPS_PER_WARP + gi) * 16;
                 if (grp_row >= valid || no_math) break;           // warp-uniform
-                const int grp_valid = valid - grp_row;            // >= 1; < 16 only in a sequence's last group
+                const int grp_valid = valid - grp_row;            // >= 1; short only in a sequence's last group
                 const int box_head = S::HEADS > 1 ? warp : 0;
-
-                wrote |= process_group<KV>(k_tile, v_tile,
-                                           [&](int t, int panel) { return row_offset<KV, S::HEADS>(t, panel, btl, box_head); },
-                                           grp_row, grp_valid, qb, acc, m_run, l_run, qk_scale, lane);
+                auto rows = [&](int t, int panel) { return row_offset<KV, S::HEADS>(t, panel, btl, box_head); };
+                if constexpr (FP8)
+                    wrote |= process_group_e4m3(k_tile, v_tile, rows, grp_row, grp_valid, qb, acc, m_run, l_run, col_scale, lane);
+                else
+                    wrote |= process_group_f16(k_tile, v_tile, rows, grp_row, grp_valid, qb, acc, m_run, l_run, qk_scale, lane);
             }
 
             // Release the stage to the producer.
@@ -833,6 +994,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         if (!alive) break;
 
         // ---- segment end: merge the warps' softmax states and write the result.
+        // Accumulator mt of a lane: dims 16mt + g (values 0, 1) and 16mt + g + 8 (values 2, 3), heads 2qd, 2qd+1.
         {
             float l[2] = {l_run[0], l_run[1]};
 #pragma unroll
@@ -842,10 +1004,14 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             }
             if constexpr (S::HEADS > 1) {
                 // Head-fused: this warp owns kv head `warp` of row sg.x outright.  Work items are rows:
-                // item_seg_begin is indexed by row, partials by (segment, query head).  Every lane
-                // normalises and stores its own fragment values; nothing is exchanged between warps.
+                // item_seg_begin is indexed by row, partials by (segment, query head).  Nothing is exchanged
+                // between warps.  A whole row goes through the warp's staging rows in shared memory so that it
+                // leaves as 16-byte stores, 512 contiguous bytes per instruction (to every peer's buffer when
+                // the output is gathered); a piece of a split row is stored as fp32 partials from the fragments.
                 const int s0 = p.item_seg_begin[sg.x], s1 = p.item_seg_begin[sg.x + 1];
                 const bool whole_row = s1 - s0 == 1;
+                __half* stage_rows = reinterpret_cast<__half*>(gen + S::OUT_STAGE_OFFSET) + warp * (GROUP * HEAD_DIM);
+                if (whole_row) __syncwarp();   // the previous row's chunks have been read
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int hd = 2 * qd + h;
@@ -853,15 +1019,13 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                         const int hq = warp * GROUP + hd;
                         const float inv = v_scale / l[h];
                         const size_t prow = (static_cast<size_t>(seg) * p.num_q_heads + hq) * HEAD_DIM;
-                        const size_t orow = out_index(p, gp, sg.x, hq);
 #pragma unroll
                         for (int mt = 0; mt < 8; mt++) {
-                            const int d0 = FP8 ? 16 * g + 2 * mt : 16 * mt + g;
-                            const int d1 = FP8 ? d0 + 1 : d0 + 8;
+                            const int d0 = 16 * mt + g, d1 = d0 + 8;
                             const float o0 = acc[mt][h] * inv, o1 = acc[mt][2 + h] * inv;
                             if (whole_row) {
-                                store_out(p, gp, orow + d0, __float2half(o0));
-                                store_out(p, gp, orow + d1, __float2half(o1));
+                                stage_rows[hd * HEAD_DIM + d0] = __float2half(o0);
+                                stage_rows[hd * HEAD_DIM + d1] = __float2half(o1);
                             } else {
                                 p.partial_out[prow + d0] = o0;
                                 p.partial_out[prow + d1] = o1;
@@ -870,6 +1034,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                         if (!whole_row && g == 0)
                             p.partial_lse[static_cast<size_t>(seg) * p.num_q_heads + hq] = m_run[h] + log2f(l[h]);
                     }
+                }
+                if (whole_row) {
+                    __syncwarp();
+                    const size_t orow = out_index(p, gp, sg.x, warp * GROUP);   // the group's heads are consecutive rows of 128
+                    for (int c = lane; c < GROUP * 16; c += 32)
+                        store_out(p, gp, orow + c * 8, *reinterpret_cast<const uint4*>(stage_rows + c * 8));
                 }
                 if (!whole_row && (p.needs_merge == MERGE_IN_KERNEL ||
                                    (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES))) {
@@ -901,37 +1071,41 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                         float* row = w_o + (warp * S::GROUP_PAD + (head - head0)) * OSTRIDE;
 #pragma unroll
                         for (int mt = 0; mt < 8; mt++) {
-                            if constexpr (FP8) {
-                                row[16 * g + 2 * mt]     = acc[mt][h];
-                                row[16 * g + 2 * mt + 1] = acc[mt][2 + h];
-                            } else {
-                                row[16 * mt + g]     = acc[mt][h];
-                                row[16 * mt + g + 8] = acc[mt][2 + h];
-                            }
+                            row[16 * mt + g]     = acc[mt][h];
+                            row[16 * mt + g + 8] = acc[mt][2 + h];
                         }
                         if (g == 0) { w_m[warp * 8 + head] = m_run[h]; w_l[warp * 8 + head] = l[h]; }
                     }
                 }
                 if (!consumer_sync()) break;
+                // every thread combines four consecutive dims of one head over the warps: the outputs leave as
+                // 8-byte (fp16 row) or 16-byte (fp32 partial) stores, 256 or 512 contiguous bytes per warp
                 constexpr int HEADS = GROUP < S::GROUP_PAD ? GROUP : S::GROUP_PAD;
-                for (int i = tid; i < HEADS * HEAD_DIM; i += S::CONSUMERS) {
-                    const int hl = i / HEAD_DIM, d = i % HEAD_DIM, hd = head0 + hl;
+                for (int i = tid; i < HEADS * (HEAD_DIM / 4); i += S::CONSUMERS) {
+                    const int hl = i / (HEAD_DIM / 4), d = (i % (HEAD_DIM / 4)) * 4, hd = head0 + hl;
                     float m_all = -INFINITY;
 #pragma unroll
                     for (int w = 0; w < C::WARPS; w++) m_all = fmaxf(m_all, w_m[w * 8 + hd]);
-                    float num = 0.f, den = 0.f;
+                    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+                    float den = 0.f;
 #pragma unroll
                     for (int w = 0; w < C::WARPS; w++) {
                         const float wt = exp2f(w_m[w * 8 + hd] - m_all);   // 0 for warps that saw no tokens
-                        num = fmaf(wt, w_o[(w * S::GROUP_PAD + hl) * OSTRIDE + d], num);
+                        const float4 o = *reinterpret_cast<const float4*>(w_o + (w * S::GROUP_PAD + hl) * OSTRIDE + d);
+                        num.x = fmaf(wt, o.x, num.x); num.y = fmaf(wt, o.y, num.y);
+                        num.z = fmaf(wt, o.z, num.z); num.w = fmaf(wt, o.w, num.w);
                         den = fmaf(wt, w_l[w * 8 + hd], den);
                     }
-                    const float o = num / den * v_scale;
+                    const float4 o = make_float4(num.x / den * v_scale, num.y / den * v_scale, num.z / den * v_scale, num.w / den * v_scale);
                     if (whole) {
-                        store_out(p, gp, out_index(p, gp, sg.x, sg.y * GROUP + hd) + d, __float2half(o));
+                        const __half2 lo = __floats2half2_rn(o.x, o.y), hi = __floats2half2_rn(o.z, o.w);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                        store_out(p, gp, out_index(p, gp, sg.x, sg.y * GROUP + hd) + d, packed);
                     } else {
                         const size_t row = static_cast<size_t>(seg) * GROUP + hd;
-                        p.partial_out[row * HEAD_DIM + d] = o;
+                        *reinterpret_cast<float4*>(p.partial_out + row * HEAD_DIM + d) = o;
                         if (d == 0) p.partial_lse[row] = m_all + log2f(den);
                     }
                 }
@@ -985,11 +1159,12 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 constexpr int MERGE_WIDE_MIN = 8;
 // One (row, query head) pair by the four warps of a CTA; s0, s1: the pair's segment range.
 template<int GROUP, bool ROW_ITEMS>
-__device__ __forceinline__ void merge_pair(const pd_params& p, int idx, int s0, int s1, float4 (*part_num)[32], float* part_den)
+__device__ __forceinline__ void merge_pair(const pd_params& p, int idx, int s0, int s1, int seg_limit, float4 (*part_num)[32], float* part_den)
 {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = idx / p.num_q_heads, hq = idx % p.num_q_heads;
     if (s1 - s0 <= 1) return;   // written directly by the decode kernel
+    if (seg_limit > 0 && s1 > seg_limit) return;   // beyond a fixed-size workspace: the decode kernel has reported it
     if (p.needs_merge == MERGE_HYBRID && s1 - s0 <= HYBRID_MAX_PIECES) return;   // merged by the decode kernel
     GatherOut local{};   // world = 0: plain output
     const int stride = ROW_ITEMS ? p.num_q_heads : GROUP;
@@ -1046,7 +1221,7 @@ __device__ __forceinline__ void merge_pair(const pd_params& p, int idx, int s0, 
 // pair is done after reading two integers (plans cut on the device).
 template<int GROUP, bool ROW_ITEMS = false, bool WALK = false>
 __global__ void __launch_bounds__(128)
-merge_segments_kernel(const __grid_constant__ pd_params p)
+merge_segments_kernel(const __grid_constant__ pd_params p, const int seg_limit)
 {
     __shared__ float4 part_num[4][32];
     __shared__ float  part_den[4];
@@ -1065,12 +1240,12 @@ merge_segments_kernel(const __grid_constant__ pd_params p)
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (static_cast<int>(blockIdx.x) >= pairs) return;
-    merge_pair<GROUP, ROW_ITEMS>(p, blockIdx.x, s0, s1, part_num, part_den);
+    merge_pair<GROUP, ROW_ITEMS>(p, blockIdx.x, s0, s1, seg_limit, part_num, part_den);
     if constexpr (WALK) {
         for (int idx = blockIdx.x + gridDim.x; idx < pairs; idx += gridDim.x) {
             __syncthreads();   // the scratch is reused
             merge_pair<GROUP, ROW_ITEMS>(p, idx, p.item_seg_begin[item_of(idx)], p.item_seg_begin[item_of(idx) + 1],
-                                         part_num, part_den);
+                                         seg_limit, part_num, part_den);
         }
     }
 }

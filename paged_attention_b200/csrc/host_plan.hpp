@@ -87,12 +87,11 @@ int build_plan(int tile, const int* seq_lens, int batch, int num_q_heads, int nu
 // them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
 // the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
 int plan_merge_mode(const pd_plan& pl) {
-    static const bool separate_merge = std::getenv("PD_B200_SEPARATE_MERGE") != nullptr;   // diagnostic
     const int items = static_cast<int>(pl.item_seg_begin.size()) - 1;
     if (static_cast<int>(pl.segments.size() / 4) <= items) return 0;
     int widest = 0;
     for (int i = 0; i < items; i++) widest = std::max(widest, pl.item_seg_begin[i + 1] - pl.item_seg_begin[i]);
-    return (separate_merge || widest > 4) ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
+    return widest > pdk::HYBRID_MAX_PIECES ? pdk::MERGE_SEPARATE : pdk::MERGE_IN_KERNEL;
 }
 
 // The planner's cut with unequal shares: CTA c owns the work units [B_c, B_{c+1}) with

@@ -51,51 +51,43 @@ int set_error(int code, const char* fmt, ...) {
                              __FILE__, __LINE__, cudaGetErrorString(e_));                  \
     } while (0)
 
-// ---- kernel variants ------------------------------------------------------------------
-// A variant fixes the CTA shape and pipeline depth for both cache dtypes.  Variant 0
-// is the default; the others exist for tuning runs (pd_set_kernel_variant).
-template<int V, typename KV> struct VariantConfig;
-// Default.  4 consumer warps + 1 producer warp per CTA, 64-token tiles.  fp16: 3 stages of
-// 32 KB, two CTAs per SM; fp8: 3 stages of 16 KB, three CTAs per SM (the fp8 widening is a
-// long dependent chain, so it wants more warps).  Both keep about 96..128 KB of copies in
-// flight per SM, where the measured load rate of the pipeline peaks; more in flight is slower.
-template<> struct VariantConfig<0, __half>        { using type = pdk::Config<4, 1, 3, 2>; };
-template<> struct VariantConfig<0, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 3, 3>; };
-// 8 consumer warps, 128-token tiles, one CTA per SM.
-template<> struct VariantConfig<1, __half>        { using type = pdk::Config<8, 1, 3, 1>; };
-template<> struct VariantConfig<1, __nv_fp8_e4m3> { using type = pdk::Config<8, 1, 6, 1>; };
-// 4 consumer warps, 64-token tiles, deep pipeline, one CTA per SM.
-template<> struct VariantConfig<2, __half>        { using type = pdk::Config<4, 1, 6, 1>; };
-template<> struct VariantConfig<2, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 12, 1>; };
-// 4 consumer warps with two 16-token groups each: 128-token tiles, one CTA per SM.
-template<> struct VariantConfig<3, __half>        { using type = pdk::Config<4, 2, 3, 1>; };
-template<> struct VariantConfig<3, __nv_fp8_e4m3> { using type = pdk::Config<4, 2, 6, 1>; };
-// Three CTAs per SM for fp16 as well; fp8 with two CTAs per SM and a deeper pipeline.
-template<> struct VariantConfig<4, __half>        { using type = pdk::Config<4, 1, 2, 3>; };
-template<> struct VariantConfig<4, __nv_fp8_e4m3> { using type = pdk::Config<4, 1, 6, 2>; };
-constexpr int NUM_VARIANTS = 5;
+// ---- kernel shapes --------------------------------------------------------------------
+// CTA shape and pipeline depth per cache dtype: Config<consumer warps, 16-token groups per warp per tile,
+// stages, CTAs per SM>.  4 consumer warps + 1 producer warp per CTA.  fp16: 64-token tiles, 3 stages of
+// 32 KB, two CTAs per SM.  Both keep about 96..128 KB of copies in flight per SM, where the measured load
+// rate of the pipeline peaks; more in flight is slower.  The two macros let a tuning build try other shapes
+// (python -m paged_attention_b200.build takes them from the environment variable PD_B200_NVCC_FLAGS).
+#ifndef PD_B200_FP16_CONFIG
+#define PD_B200_FP16_CONFIG 4, 1, 3, 2
+#endif
+#ifndef PD_B200_FP8_CONFIG
+#define PD_B200_FP8_CONFIG 4, 2, 3, 2
+#endif
+template<typename KV> struct DefaultConfig;
+template<> struct DefaultConfig<__half>        { using type = pdk::Config<PD_B200_FP16_CONFIG>; };
+template<> struct DefaultConfig<__nv_fp8_e4m3> { using type = pdk::Config<PD_B200_FP8_CONFIG>; };
 
 struct KernelInfo {
     const void* fn;
-    int tile, threads, smem, per_sm;
-    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&,
+    int tile, threads, smem, per_sm, stages;
+    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, int, unsigned*, const pdk::GatherOut&,
                    const pdk::HeadScales&, const pdk::CtaStats&, cudaStream_t);
-    void (*merge)(const pd_params&, cudaStream_t);
+    void (*merge)(const pd_params&, int, cudaStream_t);
 };
 
 template<typename KV, int GROUP, typename C>
-void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl,
+void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl, int seg_limit,
                    unsigned* status, const pdk::GatherOut& gather, const pdk::HeadScales& scales, const pdk::CtaStats& stats,
                    cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
-    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales, stats);
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, seg_limit, status, gather, scales, stats);
 }
 // The merge kernel is launched as a programmatic dependent of the decode kernel before it: its CTAs are
 // placed while the decode grid drains and wait inside the kernel (griddepcontrol.wait) until that grid is
 // complete, which takes the launch latency out of the gap between the two kernels.
 constexpr int MERGE_GRID_CAP = 148 * 8;
 template<typename Kernel>
-void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_t stream) {
+void launch_dependent(Kernel kernel, int blocks, const pd_params& p, int seg_limit, cudaStream_t stream) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(blocks));
     cfg.blockDim = dim3(128);
@@ -105,27 +97,26 @@ void launch_dependent(Kernel kernel, int blocks, const pd_params& p, cudaStream_
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, kernel, p);
+    cudaLaunchKernelEx(&cfg, kernel, p, seg_limit);
 }
 template<int GROUP>
-void launch_merge(const pd_params& p, cudaStream_t stream) {
+void launch_merge(const pd_params& p, int seg_limit, cudaStream_t stream) {
     const int pairs = p.batch * p.num_q_heads;
-    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, false, true>, MERGE_GRID_CAP, p, stream);
-    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, false, false>, pairs, p, stream);
+    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, false, true>, MERGE_GRID_CAP, p, seg_limit, stream);
+    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, false, false>, pairs, p, seg_limit, stream);
 }
 
-template<typename KV, int GROUP, int V>
+template<typename KV, int GROUP>
 KernelInfo make_info() {
-    using C = typename VariantConfig<V, KV>::type;
+    using C = typename DefaultConfig<KV>::type;
     using S = pdk::Shape<KV, GROUP, C>;
     return KernelInfo{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
-                      S::SMEM_BYTES, C::MIN_CTAS, &launch_decode<KV, GROUP, C>, &launch_merge<GROUP>};
+                      S::SMEM_BYTES, C::MIN_CTAS, C::STAGES, &launch_decode<KV, GROUP, C>, &launch_merge<GROUP>};
 }
 
-template<typename KV, int V>
+template<typename KV>
 const KernelInfo* info_by_group(int group) {
-    static const KernelInfo t[4] = {make_info<KV, 1, V>(), make_info<KV, 2, V>(), make_info<KV, 4, V>(),
-                                    make_info<KV, 8, V>()};
+    static const KernelInfo t[4] = {make_info<KV, 1>(), make_info<KV, 2>(), make_info<KV, 4>(), make_info<KV, 8>()};
     switch (group) {
         case 1: return &t[0];
         case 2: return &t[1];
@@ -145,10 +136,10 @@ template<typename KV> struct FusedConfig;
 template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>; };
 
 template<int GROUP>
-void launch_merge_rows(const pd_params& p, cudaStream_t stream) {
+void launch_merge_rows(const pd_params& p, int seg_limit, cudaStream_t stream) {
     const int pairs = p.batch * p.num_q_heads;
-    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, true, true>, MERGE_GRID_CAP, p, stream);
-    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, true, false>, pairs, p, stream);
+    if (pairs > MERGE_GRID_CAP) launch_dependent(pdk::merge_segments_kernel<GROUP, true, true>, MERGE_GRID_CAP, p, seg_limit, stream);
+    else                        launch_dependent(pdk::merge_segments_kernel<GROUP, true, false>, pairs, p, seg_limit, stream);
 }
 
 template<typename KV, int GROUP>
@@ -156,7 +147,7 @@ KernelInfo make_fused_info() {
     using C = typename FusedConfig<KV>::type;
     using S = pdk::Shape<KV, GROUP, C>;
     return KernelInfo{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
-                      S::SMEM_BYTES, C::MIN_CTAS, &launch_decode<KV, GROUP, C>, &launch_merge_rows<GROUP>};
+                      S::SMEM_BYTES, C::MIN_CTAS, C::STAGES, &launch_decode<KV, GROUP, C>, &launch_merge_rows<GROUP>};
 }
 
 template<typename KV>
@@ -179,37 +170,12 @@ int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   //
 #include "adaptive_cut.hpp"
 namespace {
 
-template<typename KV>
-const KernelInfo* info_by_variant(int variant, int group) {
-    switch (variant) {
-        case 0: return info_by_group<KV, 0>(group);
-        case 1: return info_by_group<KV, 1>(group);
-        case 2: return info_by_group<KV, 2>(group);
-        case 3: return info_by_group<KV, 3>(group);
-        case 4: return info_by_group<KV, 4>(group);
-    }
-    return nullptr;
-}
-
-int g_variant = -1;
-std::once_flag g_variant_once;
-int current_variant() {
-    std::call_once(g_variant_once, [] {
-        if (g_variant >= 0) return;
-        const char* e = std::getenv("PD_B200_VARIANT");
-        const int v = e ? std::atoi(e) : 0;
-        g_variant = (v >= 0 && v < NUM_VARIANTS) ? v : 0;
-    });
-    return g_variant;
-}
-
 // Same argument checks, in the same order, as the reference's dispatch
 // (src/decode/decode.cu:18-39): head_dim first, then the group size.
 int find_kernel(int dtype, int head_dim, int group, const KernelInfo** out) {
     if (dtype != PD_FP16 && dtype != PD_FP8_E4M3) return set_error(PD_INVALID_ARGUMENT, "unsupported KV dtype %d", dtype);
     if (head_dim != 128) return set_error(PD_INVALID_ARGUMENT, "unsupported head_dim %d", head_dim);
-    const KernelInfo* k = dtype == PD_FP16 ? info_by_variant<__half>(current_variant(), group)
-                                           : info_by_variant<__nv_fp8_e4m3>(current_variant(), group);
+    const KernelInfo* k = dtype == PD_FP16 ? info_by_group<__half>(group) : info_by_group<__nv_fp8_e4m3>(group);
     if (!k) return set_error(PD_INVALID_ARGUMENT, "unsupported GQA group size %d", group);
     *out = k;
     return PD_OK;
@@ -280,11 +246,7 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
         return set_error(PD_INVALID_ARGUMENT, "KV pool pointer must be 16-byte aligned");
     const cuuint64_t pages = num_pages > 0 ? static_cast<cuuint64_t>(num_pages) : (1ull << 31);
     const cuuint64_t row = dtype == PD_FP16 ? 256 : 128;
-    static const int promo_env = std::getenv("PD_B200_L2PROMO") ? std::atoi(std::getenv("PD_B200_L2PROMO")) : 3;
-    const CUtensorMapL2promotion promo = promo_env == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
-                                       : promo_env == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
-                                       : promo_env == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                                                        : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
+    const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     CUresult r;
     if (dtype == PD_FP16) {
         const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
@@ -348,6 +310,10 @@ struct pd_device_plan {
     } fused,
       weighted;                    // the caller's (row, kv head) schedule cut in unequal shares (adaptive cut)
     unsigned long long* stats = nullptr;       // record of launches that run the caller's plan as it is
+    // Per schedule region: the LSE array and the arrival counters of the in-kernel merge behind it (what
+    // pd_device_plan_reset clears; the counters' exact start follows the plan's real segment count, which for
+    // plans cut on the device only the device knows, so the whole tail of the region is cleared).
+    struct Tail { void* ptr = nullptr; size_t bytes = 0; } tails[3];
 };
 
 namespace {
@@ -383,6 +349,8 @@ struct pd_cache {
     void*  batch_device = nullptr;
     size_t batch_cap = 0;
     cudaEvent_t batch_staged = nullptr;
+    cudaEvent_t batch_done = nullptr;     // the last batched append's kernels (release waits for them)
+    bool batch_pending = false;
 };
 
 extern "C" {
@@ -448,14 +416,6 @@ int pd_adaptive_cut_reset(void) {
     return PD_OK;
 }
 
-int pd_set_kernel_variant(int variant) {
-    if (variant < 0 || variant >= NUM_VARIANTS) return set_error(PD_INVALID_ARGUMENT, "kernel variant %d does not exist", variant);
-    current_variant();   // consume the once-flag so the environment cannot override later
-    g_variant = variant;
-    return PD_OK;
-}
-int pd_kernel_variant(void) { return current_variant(); }
-
 int pd_tile_tokens(int dtype, int head_dim, int group, int* out) {
     const KernelInfo* k;
     if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
@@ -475,7 +435,7 @@ int pd_wave_ctas(int dtype, int head_dim, int group, int* out) {
     return PD_OK;
 }
 
-// One wave at the residency the variant was shaped for (never more than fits).
+// One wave at the residency the kernel was shaped for (never more than fits).
 int pd_default_ctas(int dtype, int head_dim, int group, int* out) {
     const KernelInfo* k;
     if (int rc = find_kernel(dtype, head_dim, group, &k)) return rc;
@@ -649,6 +609,9 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         fk = fused_info<__half>(group);
         int grid = plan->forced_ctas;
         if (fk && grid <= 0) grid = fused_wave(fk);
+        // a plan rebuilt from a caller's arrays does not say whether its grid was asked for; a grid smaller
+        // than one CTA per SM is taken as asked for (sharing the GPU, a sweep) and kept
+        if (fk && plan->dtype == -2 && plan->num_ctas > 0 && plan->num_ctas < grid) grid = plan->num_ctas;
         if (!fk || grid <= 0 ||
             build_plan(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
             rows_plan = nullptr;
@@ -663,11 +626,11 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     if (g_adaptive && plan->batch > 0 && static_cast<int>(plan->seq_lens.size()) == plan->batch) {
         if (fused_runs) {
             RateTable* t = rate_table(fk->fn, rows_plan->num_ctas);
-            update_weights(t, stream);
+            const std::vector<float> weights = update_weights(t, stream);
             if (t) stats_fused = t->slots;
-            if (t && !t->weights.empty()) {
+            if (t && !weights.empty()) {
                 pd_plan* w = nullptr;
-                if (build_plan_weighted(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, t->weights, &w) == PD_OK) {
+                if (build_plan_weighted(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, weights, &w) == PD_OK) {
                     delete rows_plan;
                     rows_plan = w;
                 }
@@ -677,10 +640,10 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
             if (find_kernel(plan->dtype, head_dim, group, &sk) == PD_OK && sk->tile == plan->tile && plan->num_ctas > 0 &&
                 plan->num_kv_heads > 0 && plan->num_q_heads / plan->num_kv_heads == group) {
                 RateTable* t = rate_table(sk->fn, plan->num_ctas);
-                update_weights(t, stream);
+                const std::vector<float> weights = update_weights(t, stream);
                 if (t) stats_std = t->slots;
-                if (t && !t->weights.empty() &&
-                    build_plan_weighted(plan->tile, plan->seq_lens.data(), plan->batch, plan->num_kv_heads, t->weights,
+                if (t && !weights.empty() &&
+                    build_plan_weighted(plan->tile, plan->seq_lens.data(), plan->batch, plan->num_kv_heads, weights,
                                         &weighted_plan) != PD_OK)
                     weighted_plan = nullptr;
             }
@@ -766,8 +729,11 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // them itself (one warp per split row); a row cut in dozens of pieces (one long sequence spread over
     // the whole grid) merges faster in the separate kernel, which puts a warp on every (row, query head).
     dp->needs_merge = plan_merge_mode(*plan);
-    if (plan->num_items)
+    for (auto& t : dp->tails) t = pd_device_plan::Tail{};
+    if (plan->num_items) {
+        dp->tails[0] = {dp->partial + rows * head_dim, sizeof(float) * (rows + plan->num_items)};
         PD_CUDA(cudaMemsetAsync(dp->partial + rows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
+    }
 
     dp->fused = pd_device_plan::Fused{};
     if (rows_plan) {
@@ -783,6 +749,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         f.cta_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes);
         f.row_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes + fcta_bytes);
         f.partial_out = dp->partial + std_need;
+        dp->tails[1] = {f.partial_out + frows * head_dim, sizeof(float) * (frows + plan->num_items)};
         PD_CUDA(cudaMemsetAsync(f.partial_out + frows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     }
     dp->weighted = pd_device_plan::Fused{};
@@ -800,6 +767,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         f.row_seg_begin = reinterpret_cast<const int*>(a + alt_bytes + wseg_bytes + wcta_bytes);   // (row, kv head) items
         f.partial_out = dp->partial + std_need + f_need;
         f.stats = stats_std;
+        dp->tails[2] = {f.partial_out + wrows * head_dim, sizeof(float) * (wrows + plan->num_items)};
         PD_CUDA(cudaMemsetAsync(f.partial_out + wrows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     }
     {
@@ -886,6 +854,8 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     dp->fused           = pd_device_plan::Fused{};
     dp->weighted        = pd_device_plan::Fused{};
     dp->stats           = nullptr;
+    for (auto& t : dp->tails) t = pd_device_plan::Tail{};
+    dp->tails[0] = {dp->partial_lse, sizeof(float) * (rows + items)};
     pdk::PlanJob job{};
     job.seq_lens = d_seq_lens; job.slot_ids = d_slot_ids;
     job.batch = batch; job.num_kv_heads = num_kv_heads; job.tile = k->tile; job.grid = grid;
@@ -935,6 +905,7 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         fj.row_tile_begin = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + frow_bytes);
         fj.info = reinterpret_cast<int*>(fa + fseg_bytes + fcta_bytes + 2 * frow_bytes);
         fj.partial_lse = f.partial_out + frows * head_dim;
+        dp->tails[1] = {f.partial_out + frows * head_dim, sizeof(float) * (frows + items)};
         if (g_adaptive && batch > 0) {
             if (RateTable* t = rate_table(fk->fn, fgrid, !capturing)) {
                 if (!capturing) update_weights(t, stream);
@@ -1000,11 +971,71 @@ int pd_device_plan_bind(const pd_device_plan* dp, pd_params* p) {
     return PD_OK;
 }
 
+// After a PD_KERNEL_TIMEOUT: a CTA that gave up on a bounded wait skipped its arrivals, so the counters of
+// the in-kernel merge may hold partial counts that the next launch of the same plan would trip over.
+int pd_device_plan_reset(pd_device_plan* dp, void* stream_) {
+    if (!dp) return set_error(PD_INVALID_ARGUMENT, "device_plan_reset: null argument");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    for (const auto& t : dp->tails)
+        if (t.ptr && t.bytes) PD_CUDA(cudaMemsetAsync(t.ptr, 0, t.bytes, stream));
+    return PD_OK;
+}
+
 // ---- decode -----------------------------------------------------------------------------------------------
 
 }  // extern "C"
 
 namespace {
+// Which schedule a decode of these params runs.  The plan they were bound to (pd_device_plan_bind) may carry,
+// next to the caller's (row, kv head) cut, the same step cut by rows for the head-fused kernel (fp16, 8 kv
+// heads, plan made by pd_make_plan) and the caller's cut in unequal shares (adaptive cut); they are found
+// through the address of the bound segment array.  Params that point at arrays of the caller's own run as
+// they are.
+struct Selection {
+    const pd_params* params;
+    const KernelInfo* kernel;
+    int box_heads;                 // kv heads per TMA box: 1, or 8 for the head-fused kernel
+    int schedule;                  // 0 the caller's plan, 1 head-fused rows, 2 the caller's plan in unequal shares
+    unsigned long long* stats;
+};
+Selection select_schedule(int dtype, const pd_params* p, const KernelInfo* k, bool gathered, pd_params* scratch) {
+    Selection sel{p, k, 1, 0, nullptr};
+    AltSchedules alt;
+    {
+        std::lock_guard<std::mutex> lock(g_fused_mutex);
+        auto it = g_fused_registry.find(p->segments);
+        if (it == g_fused_registry.end()) return sel;
+        alt = it->second;
+    }
+    const int group = p->num_q_heads / p->num_kv_heads;
+    auto matches = [&](const pd_device_plan::Fused& f) {
+        return f.valid && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch && f.group == group;
+    };
+    const KernelInfo* fk = dtype == PD_FP16 && p->num_kv_heads == FUSED_HEADS ? fused_info<__half>(group) : nullptr;
+    // Head-fused, mode 1: not where rows would be spread over more than 4 CTAs each.
+    const bool use_fused = fk && g_head_fused && matches(alt.fused) &&
+                           (g_head_fused == 2 || alt.fused.needs_merge != pdk::MERGE_SEPARATE);
+    const bool use_weighted = !use_fused && g_adaptive && matches(alt.weighted);
+    if (g_adaptive && !use_fused && !use_weighted) sel.stats = alt.stats;
+    if (use_fused || use_weighted) {
+        const pd_device_plan::Fused& f = use_fused ? alt.fused : alt.weighted;
+        *scratch = *p;
+        scratch->segments = f.segments;
+        scratch->cta_seg_begin = f.cta_seg_begin;
+        scratch->item_seg_begin = f.row_seg_begin;       // work items: rows (head-fused) or (row, kv head)
+        scratch->num_ctas = f.num_ctas;
+        scratch->needs_merge = f.needs_merge;            // this schedule has its own splits
+        if (gathered && scratch->needs_merge) scratch->needs_merge = pdk::MERGE_IN_KERNEL;   // gathered rows are written by the decode kernel
+        scratch->partial_out = f.partial_out;
+        scratch->partial_lse = f.partial_out + f.rows * p->head_dim;
+        sel.params = scratch;
+        sel.schedule = use_fused ? 1 : 2;
+        if (use_fused) { sel.kernel = fk; sel.box_heads = FUSED_HEADS; }
+        if (g_adaptive) sel.stats = f.stats;
+    }
+    return sel;
+}
+
 int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherOut& gather, void* stream_,
                 const pdk::HeadScales& scales = pdk::HeadScales{nullptr, nullptr}) {
     if (!p) return set_error(PD_INVALID_ARGUMENT, "paged_decode: null params");
@@ -1019,55 +1050,14 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: null device pointer");
     if (p->needs_merge && (!p->partial_out || !p->partial_lse))
         return set_error(PD_INVALID_ARGUMENT, "paged_decode: split rows need the partial workspace");
-    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0)
-        return set_error(PD_INVALID_ARGUMENT, "paged_decode: q must be 16-byte aligned");
-    // Head-fused schedule: taken when the plan these params were bound to carries one (see
-    // pd_device_plan_upload), i.e. the layer has 8 kv heads and the plan came from pd_make_plan.
-    // needs_merge < 0 (diagnostic): run the decode kernel only and leave split rows unmerged.
-    pd_params fused_params;
-    pd_params unmerged;
-    if (p->needs_merge < 0) {
-        unmerged = *p;
-        unmerged.needs_merge = 0;
-    }
-    const bool skip_merge = p->needs_merge < 0;
-    int box_heads = 1;
-    unsigned long long* stats_slots = nullptr;
-    {
-        AltSchedules alt;
-        bool found = false;
-        {
-            std::lock_guard<std::mutex> lock(g_fused_mutex);
-            auto it = g_fused_registry.find(p->segments);
-            if (it != g_fused_registry.end()) { alt = it->second; found = true; }
-        }
-        const int group = p->num_q_heads / p->num_kv_heads;
-        auto matches = [&](const pd_device_plan::Fused& f) {
-            return f.valid && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch && f.group == group;
-        };
-        const KernelInfo* fk = dtype == PD_FP16 && p->num_kv_heads == FUSED_HEADS ? fused_info<__half>(group) : nullptr;
-        // Head-fused, mode 1: not where rows would be spread over more than 4 CTAs each.
-        const bool use_fused = found && fk && g_head_fused && matches(alt.fused) &&
-                               (g_head_fused == 2 || alt.fused.needs_merge != pdk::MERGE_SEPARATE);
-        const bool use_weighted = found && !use_fused && g_adaptive && matches(alt.weighted);
-        if (found && g_adaptive && !use_fused && !use_weighted) stats_slots = alt.stats;
-        if (use_fused || use_weighted) {
-            const pd_device_plan::Fused& f = use_fused ? alt.fused : alt.weighted;
-            fused_params = *p;
-            fused_params.segments = f.segments;
-            fused_params.cta_seg_begin = f.cta_seg_begin;
-            fused_params.item_seg_begin = f.row_seg_begin;       // work items: rows (head-fused) or (row, kv head)
-            fused_params.num_ctas = f.num_ctas;
-            fused_params.needs_merge = p->needs_merge < 0 ? 0 : f.needs_merge;   // this schedule has its own splits
-            if (gather.world && fused_params.needs_merge) fused_params.needs_merge = pdk::MERGE_IN_KERNEL;   // gathered rows are written by the decode kernel
-            fused_params.partial_out = f.partial_out;
-            fused_params.partial_lse = f.partial_out + f.rows * p->head_dim;
-            p = &fused_params;
-            if (use_fused) { k = fk; box_heads = FUSED_HEADS; }
-            if (g_adaptive) stats_slots = f.stats;
-        }
-    }
-    if (skip_merge && p != &fused_params) p = &unmerged;
+    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0 || reinterpret_cast<uintptr_t>(p->out) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode: q and out must be 16-byte aligned");
+    pd_params alt_params;
+    Selection sel = select_schedule(dtype, p, k, gather.world != 0, &alt_params);
+    p = sel.params;
+    k = sel.kernel;
+    const int box_heads = sel.box_heads;
+    unsigned long long* stats_slots = sel.stats;
     if (int rc = configure(k)) return rc;
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
@@ -1081,15 +1071,10 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    static const bool load_only = std::getenv("PD_B200_LOAD_ONLY") != nullptr;   // diagnostic, see decode_kernel.cuh
-    static const bool no_hint = std::getenv("PD_B200_NO_L2_HINT") != nullptr;
-    static const int stage_limit = std::getenv("PD_B200_STAGE_LIMIT") ? (std::atoi(std::getenv("PD_B200_STAGE_LIMIT")) & 0xf) : 0;
-    k->launch(*p, k_map, v_map,
-              btl | (load_only ? pdk::FLAG_LOAD_ONLY : 0) | (no_hint ? pdk::FLAG_NO_L2_HINT : 0) | (stage_limit << 12),
-              status, gather, scales, pdk::CtaStats{stats_slots}, stream);
+    k->launch(*p, k_map, v_map, btl, 0, status, gather, scales, pdk::CtaStats{stats_slots}, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
-        k->merge(*p, stream);
+        k->merge(*p, 0, stream);
         PD_CUDA(cudaGetLastError());
     }
     return PD_OK;
@@ -1109,6 +1094,25 @@ int pd_paged_decode(int dtype, const pd_params* p, void* stream) {
 int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const float* d_k_scales, const float* d_v_scales,
                            void* stream) {
     return decode_impl(dtype, p, num_pages, pdk::GatherOut{}, stream, pdk::HeadScales{d_k_scales, d_v_scales});
+}
+
+int pd_describe_launch(int dtype, const pd_params* p, int* out) {
+    if (!p || !out) return set_error(PD_INVALID_ARGUMENT, "describe_launch: null argument");
+    if (p->num_kv_heads <= 0 || p->num_q_heads % p->num_kv_heads != 0)
+        return set_error(PD_INVALID_ARGUMENT, "num_q_heads must be a multiple of num_kv_heads");
+    const KernelInfo* k;
+    if (int rc = find_kernel(dtype, p->head_dim, p->num_q_heads / p->num_kv_heads, &k)) return rc;
+    pd_params scratch;
+    const Selection sel = select_schedule(dtype, p, k, false, &scratch);
+    out[0] = sel.schedule;
+    out[1] = sel.params->num_ctas;
+    out[2] = sel.kernel->tile;
+    out[3] = sel.box_heads;
+    out[4] = sel.kernel->threads / 32 - 1;
+    out[5] = sel.kernel->stages;
+    out[6] = sel.kernel->per_sm;
+    out[7] = sel.params->needs_merge;
+    return PD_OK;
 }
 
 // ---- decode without any allocation -------------------------------------------------------------------------
@@ -1188,8 +1192,8 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     const StaticScratch* scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
 
-    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0)
-        return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: q must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(p->q) % 16 != 0 || reinterpret_cast<uintptr_t>(p->out) % 16 != 0)
+        return set_error(PD_INVALID_ARGUMENT, "paged_decode_static: q and out must be 16-byte aligned");
     pd_params local = *p;                       // same launch, workspace redirected to the built-in array
     local.partial_out = scratch->partials;
     local.partial_lse = scratch->partials + rows * p->head_dim;
@@ -1203,11 +1207,14 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(local, k_map, v_map, btl, d_status ? d_status : scratch->status, pdk::GatherOut{}, pdk::HeadScales{nullptr, nullptr},
-              pdk::CtaStats{nullptr}, stream);
+    // The kernels compare the declared count with the plan they walk (cta_seg_begin on the device): a CTA
+    // whose segments lie beyond it stores nothing and reports ST_WORKSPACE instead of writing past the array.
+    const int seg_limit = std::max(num_segments, 1);
+    k->launch(local, k_map, v_map, btl, seg_limit, d_status ? d_status : scratch->status, pdk::GatherOut{},
+              pdk::HeadScales{nullptr, nullptr}, pdk::CtaStats{nullptr}, stream);
     PD_CUDA(cudaGetLastError());
     if (local.needs_merge) {
-        k->merge(local, stream);
+        k->merge(local, seg_limit, stream);
         PD_CUDA(cudaGetLastError());
     }
     return PD_OK;
@@ -1221,23 +1228,15 @@ int pd_kernel_status(void* stream, unsigned* out) {
     PD_CUDA(cudaMemcpy(out, status, sizeof(unsigned), cudaMemcpyDeviceToHost));
     if (*out) {
         PD_CUDA(cudaMemset(status, 0, sizeof(unsigned)));
+        if ((*out >> 24) == pdk::ST_WORKSPACE)
+            return set_error(PD_KERNEL_TIMEOUT, "decode kernel: the plan has more segments than the workspace holds (CTA %u gave up)",
+                             *out & 0xffffffu);
         return set_error(PD_KERNEL_TIMEOUT, "decode kernel: bounded wait %u expired in CTA %u", *out >> 24, *out & 0xffffffu);
     }
     return PD_OK;
 }
 
 // ---- bandwidth probe ---------------------------------------------------------------------------------------
-
-int pd_stream_read_pattern(const void* d_buf, size_t bytes, int blocks, int pattern, void* stream_) {
-    if (!d_buf || bytes < 16 || blocks <= 0 || reinterpret_cast<uintptr_t>(d_buf) % 16 != 0)
-        return set_error(PD_INVALID_ARGUMENT, "stream_read: bad argument");
-    unsigned* sink = nullptr;
-    if (int rc = status_word(&sink)) return rc;
-    pdk::stream_read_pattern_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream_)>>>(
-        static_cast<const uint4*>(d_buf), bytes / 16, pattern, sink);
-    PD_CUDA(cudaGetLastError());
-    return PD_OK;
-}
 
 int pd_stream_read(const void* d_buf, size_t bytes, int blocks, void* stream_) {
     if (!d_buf || bytes < 16 || blocks <= 0 || reinterpret_cast<uintptr_t>(d_buf) % 16 != 0)
@@ -1288,22 +1287,27 @@ int pd_append_tokens(int dtype, const void* d_k, const void* d_v, void* k_cache,
 
 // ---- outputs gathered over the GPUs of a node by peer stores ---------------------------------------------------
 //
-// One process per GPU.  Each rank allocates one block: two gathered-output buffers (alternating
-// per step, so a fast rank never overwrites what a slow peer is still reading from the previous
-// step), one flag per peer, one CTA counter.  Blocks are exchanged as CUDA IPC handles; after
-// pd_gather_connect every rank can store into every peer's block.
+// One process per GPU.  Each rank allocates one block: GATHER_BUFFERS gathered-output buffers used in
+// rotation (step e fills buffer e mod 4), one flag per peer, one CTA counter.  Blocks are exchanged as
+// CUDA IPC handles; after pd_gather_connect every rank can store into every peer's block.
+// Why four buffers: a rank may run step e+1's decode before it waits for step e's rows (the wait then
+// overlaps the next decode).  Its stream order is d(e+1), w(e), use(e), d(e+2), w(e+1), ...; a peer's
+// d(e+4) overwrites buffer e mod 4 and is ordered after that peer's w(e+2), i.e. after this rank's d(e+2)
+// has finished, which in this rank's stream comes after use(e).  With the wait directly behind every
+// decode two buffers would do.
 
 } // extern "C"
 
+constexpr unsigned GATHER_BUFFERS = 4;
 struct pd_gather_group {
     int world = 0, rank = 0;
     size_t out_bytes = 0, block_bytes = 0;
     unsigned epoch = 0;
-    bool wait_in_kernel = true;
+    bool wait_in_kernel = false;
     char* block[pdk::MAX_GATHER] = {};      // block[rank] is the local allocation, the rest are IPC mappings
     bool connected = false;
-    size_t flags_offset() const { return 2 * out_bytes; }
-    size_t done_offset() const { return 2 * out_bytes + 128; }
+    size_t flags_offset() const { return GATHER_BUFFERS * out_bytes; }
+    size_t done_offset() const { return GATHER_BUFFERS * out_bytes + 128; }
 };
 
 extern "C" {
@@ -1314,7 +1318,7 @@ int pd_gather_create(int world, int rank, size_t out_bytes, pd_gather_group** ou
     pd_gather_group* g = new pd_gather_group();
     g->world = world; g->rank = rank;
     g->out_bytes = (out_bytes + 255) & ~static_cast<size_t>(255);
-    g->block_bytes = 2 * g->out_bytes + 256;
+    g->block_bytes = GATHER_BUFFERS * g->out_bytes + 256;
     void* b = nullptr;
     cudaError_t e = cudaMalloc(&b, g->block_bytes);
     if (e == cudaSuccess) e = cudaMemset(b, 0, g->block_bytes);
@@ -1365,8 +1369,8 @@ int pd_gather_connect(pd_gather_group* g, const unsigned char* all_handles) {
 
 void* pd_gather_buffer(const pd_gather_group* g, int which) {
     if (!g) return nullptr;
-    const unsigned parity = which < 0 ? (g->epoch & 1u) : static_cast<unsigned>(which & 1);
-    return g->block[g->rank] + parity * g->out_bytes;
+    const unsigned index = which < 0 ? g->epoch % GATHER_BUFFERS : static_cast<unsigned>(which) % GATHER_BUFFERS;
+    return g->block[g->rank] + index * g->out_bytes;
 }
 
 unsigned pd_gather_epoch(const pd_gather_group* g) { return g ? g->epoch : 0; }
@@ -1387,7 +1391,7 @@ int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gath
     go.epoch = g->epoch;
     go.wait_in_kernel = g->wait_in_kernel ? 1 : 0;
     for (int r = 0; r < g->world; r++) {
-        go.out[r]   = reinterpret_cast<__half*>(g->block[r] + (g->epoch & 1u) * g->out_bytes);
+        go.out[r]   = reinterpret_cast<__half*>(g->block[r] + (g->epoch % GATHER_BUFFERS) * g->out_bytes);
         go.flags[r] = reinterpret_cast<unsigned*>(g->block[r] + g->flags_offset());
     }
     go.done = reinterpret_cast<unsigned*>(g->block[g->rank] + g->done_offset());
@@ -1399,6 +1403,14 @@ int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gath
     const int rc = decode_impl(dtype, &local, num_pages, go, stream);
     if (rc != PD_OK) g->epoch--;
     return rc;
+}
+
+// After a PD_KERNEL_TIMEOUT: a CTA that gave up never counted itself, so the grid counter may be left
+// between zero and the grid size; the next launch would then signal the peers too early or never.
+int pd_gather_reset(pd_gather_group* g, void* stream) {
+    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_reset: null argument");
+    PD_CUDA(cudaMemsetAsync(g->block[g->rank] + g->done_offset(), 0, sizeof(unsigned), static_cast<cudaStream_t>(stream)));
+    return PD_OK;
 }
 
 int pd_gather_set_wait_in_kernel(pd_gather_group* g, int on) {
@@ -1442,6 +1454,7 @@ void pd_cache_destroy(pd_cache* c) {
     cudaFree(c->d_slot_ids);
     cudaFree(c->d_head_scales);
     if (c->batch_staged) { cudaEventSynchronize(c->batch_staged); cudaEventDestroy(c->batch_staged); }
+    if (c->batch_done) { cudaEventSynchronize(c->batch_done); cudaEventDestroy(c->batch_done); }
     cudaFreeHost(c->batch_staging);
     cudaFree(c->batch_device);
     pd_plan_free(c->plan);
@@ -1632,12 +1645,22 @@ int pd_cache_append_batch(pd_cache* c, int count, const int* slots, const void* 
                 static_cast<int>(units), c->d_k, c->d_v, c->cfg.num_kv_heads, ps, ik, iv, hs);
         PD_CUDA(cudaGetLastError());
     }
+    if (!c->batch_done) PD_CUDA(cudaEventCreateWithFlags(&c->batch_done, cudaEventDisableTiming));
+    PD_CUDA(cudaEventRecord(c->batch_done, stream));
+    c->batch_pending = true;
     return PD_OK;
 }
 
 int pd_cache_release(pd_cache* c, int slot) {
     if (!c || slot < 0 || slot >= c->cfg.max_slots || !c->occupied[slot])
         return set_error(PD_INVALID_ARGUMENT, "release: slot is not admitted");
+    // A batched append is stream-ordered and may still be on its way (table updates, token scatter) on a
+    // stream the memset below is not ordered with; the slot's pages must not go back to the free list, nor its
+    // device-side length to zero, before that append has landed.
+    if (c->batch_pending) {
+        PD_CUDA(cudaEventSynchronize(c->batch_done));
+        c->batch_pending = false;
+    }
     for (int page : c->tables[slot]) c->free_pages.push_back(page);   // in table order
     c->tables[slot].clear();
     c->seq_lens[slot] = 0;
@@ -1733,6 +1756,17 @@ int pd_cache_run(pd_cache* c, const void* d_q, void* d_out, void* stream) {
     pd_device_plan_bind(c->device_plan, &p);
     return pd_paged_decode_scaled(c->cfg.dtype, &p, c->cfg.num_pages, c->d_head_scales,
                                   c->d_head_scales ? c->d_head_scales + c->cfg.num_kv_heads : nullptr, stream);
+}
+
+int pd_cache_describe_launch(const pd_cache* c, int* out) {
+    if (!c || !out) return set_error(PD_INVALID_ARGUMENT, "describe_launch: null argument");
+    if (!c->plan && !c->plan_on_device) return set_error(PD_INVALID_ARGUMENT, "describe_launch: no plan; call plan() first");
+    pd_params p;
+    pd_cache_params(c, &p);
+    p.batch = c->plan_batch;
+    p.num_q_heads = c->plan_num_q_heads;
+    pd_device_plan_bind(c->device_plan, &p);
+    return pd_describe_launch(c->cfg.dtype, &p, out);
 }
 
 int pd_cache_set_head_scales(pd_cache* c, const float* k_scales, const float* v_scales) {

@@ -27,50 +27,4 @@ stream_read_kernel(const uint4* __restrict__ x, size_t n, unsigned* sink)
     if (acc == 0x12345678u) *sink = acc;
 }
 
-// Diagnostic access patterns for the same read: every block streams its OWN contiguous
-// slice of the buffer (pattern 1), or visits the 4 KB chunks of its slice in a scrambled
-// order (pattern 2, what scattered 16-token fp16 pages look like to DRAM), 2 KB chunks (3).
-__global__ void __launch_bounds__(512)
-stream_read_pattern_kernel(const uint4* __restrict__ x, size_t n, int pattern, unsigned* sink)
-{
-    uint32_t acc = 0;
-    if (pattern >= 100) {
-        // teams of T = pattern - 100 consecutive blocks share one contiguous slice and take its
-        // 32 KB chunks round-robin: fewer, denser streams than one slice per block
-        const int T = pattern - 100;
-        const size_t teams = gridDim.x / T, team = blockIdx.x / T, member = blockIdx.x % T;
-        const size_t per_team = n / teams;
-        const uint4* tbase = x + per_team * team;
-        constexpr size_t CH = 2048;                      // uint4 per 32 KB chunk = 512 threads x 4 loads
-        for (size_t c = member; (c + 1) * CH <= per_team; c += T) {
-            uint4 v[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) v[k] = __ldcs(tbase + c * CH + k * 512 + threadIdx.x);
-#pragma unroll
-            for (int k = 0; k < 4; k++) acc ^= v[k].x ^ v[k].y ^ v[k].z ^ v[k].w;
-        }
-        if (acc == 0x12345678u) *sink = acc;
-        return;
-    }
-    const size_t per_block = n / gridDim.x;              // uint4 per block
-    const uint4* base = x + per_block * blockIdx.x;
-    const int chunk = pattern == 3 ? 128 : 256;          // uint4 per chunk: 2 KB or 4 KB
-    const size_t nchunks = per_block / chunk;            // scrambled with an odd multiplier when a power of two
-    const int per_iter = 512 * 4 / chunk;                // chunks covered per iteration by the block (4 loads/thread)
-    for (size_t c0 = 0; c0 + per_iter <= nchunks; c0 += per_iter) {
-        uint4 v[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const size_t lin = c0 * chunk + k * 512 + threadIdx.x;   // position inside this iteration's window
-            size_t ci = lin / chunk;
-            const size_t off = lin % chunk;
-            if (pattern >= 2) ci = (ci * 2654435761ull + 12345) % nchunks;
-            v[k] = __ldcs(base + ci * chunk + off);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; k++) acc ^= v[k].x ^ v[k].y ^ v[k].z ^ v[k].w;
-    }
-    if (acc == 0x12345678u) *sink = acc;
-}
-
 }  // namespace pdk

@@ -60,14 +60,6 @@ def default_ctas(dtype, head_dim, group):
     return _out_int(_lib.lib().pd_default_ctas, int(dtype), head_dim, group)
 
 
-def set_kernel_variant(v):
-    check(_lib.lib().pd_set_kernel_variant(v))
-
-
-def kernel_variant():
-    return _lib.lib().pd_kernel_variant()
-
-
 def set_head_fused(mode):
     """Head-fused schedule of fp16 layers with 8 kv heads: 0 / False never, 1 / True where it wins
     (the default), 2 whenever the layer allows it."""
@@ -215,6 +207,11 @@ class DevicePlan:
     def bind(self, params):
         check(_lib.lib().pd_device_plan_bind(self._h, C.byref(params)))
 
+    def reset(self, stream=0):
+        """After a KernelTimeout: clear the arrival counters of the in-kernel merge, which the CTA that gave
+        up has left short (not in the reference, whose kernels have no bounded waits)."""
+        check(_lib.lib().pd_device_plan_reset(self._h, stream))
+
     def build(self, dtype, d_seq_lens, batch, num_q_heads, num_kv_heads, head_dim=128, num_ctas=0, d_slot_ids=None,
               stream=0):
         """Cut the step's plan on the device from device-resident lengths (no counterpart in the
@@ -247,12 +244,32 @@ def paged_decode(dtype, params, stream=0, num_pages=0, d_k_scales=None, d_v_scal
                                                 stream))
 
 
-def paged_decode_static(dtype, params, num_segments, stream=0, num_pages=0, d_status=None):
+def paged_decode_static(dtype, params, plan, stream=0, num_pages=0, d_status=None):
     """Decode + merge with the library's built-in split-row workspace instead of params.partial_out /
     partial_lse: no device allocation happens in this call (there is no counterpart in the reference).
     For callers whose process has no HBM left to allocate from, or whose step loop forbids
-    cudaMalloc/cudaFree.  Raises InvalidArgument when the plan needs more than the built-in 8 MiB."""
+    cudaMalloc/cudaFree.  `plan` is the DecodePlan the params were bound from: its segment count sizes the
+    workspace (an integer count is accepted too; the kernels check it against the plan they walk and report
+    status code 6 instead of storing outside the workspace).  Raises InvalidArgument when the plan needs
+    more than the built-in 8 MiB."""
+    num_segments = plan.num_segments if hasattr(plan, "num_segments") else int(plan)
     check(_lib.lib().pd_paged_decode_static(int(dtype), C.byref(params), num_segments, num_pages, _ptr(d_status), stream))
+
+
+LAUNCH_SCHEDULES = ("caller's plan", "head-fused rows", "caller's plan in adaptive shares")
+
+
+def describe_launch(dtype, params):
+    """What a decode of these params would launch: dict with the schedule, grid, tile and kernel shape."""
+    out = (C.c_int * 8)()
+    check(_lib.lib().pd_describe_launch(int(dtype), C.byref(params), out))
+    return _launch_dict(out)
+
+
+def _launch_dict(out):
+    return {"schedule": LAUNCH_SCHEDULES[out[0]], "grid": out[1], "tile_tokens": out[2], "kv_heads_per_tile": out[3],
+            "consumer_warps": out[4], "stages": out[5], "ctas_per_sm": out[6],
+            "merge": ("none", "merge kernel", "inside the decode kernel", "per row: in-kernel up to 4 pieces, else merge kernel")[out[7]]}
 
 
 def kernel_status(stream=0):
@@ -374,6 +391,12 @@ class PagedKVCache:
     def decode(self, d_q, d_out, batch, num_q_heads, num_ctas=0, stream=0):
         check(_lib.lib().pd_cache_decode(self._h, _ptr(d_q), _ptr(d_out), batch, num_q_heads, num_ctas, stream))
 
+    def describe_launch(self):
+        """What the next run() of the current plan launches (see describe_launch)."""
+        out = (C.c_int * 8)()
+        check(_lib.lib().pd_cache_describe_launch(self._h, out))
+        return _launch_dict(out)
+
     def last_plan(self):
         h = _lib.lib().pd_cache_last_plan(self._h)
         return DecodePlan(C.c_void_p(h), owned=False) if h else None
@@ -416,5 +439,5 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "set_kernel_variant", "kernel_variant", "set_head_fused", "head_fused",
+           "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "describe_launch", "set_head_fused", "head_fused",
            "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_refresh", "adaptive_cut_tables"]

@@ -154,8 +154,9 @@ class GatherGroup:
                                                                row_stride_heads, head_offset, row_offset, stream))
 
     def set_wait_in_kernel(self, on):
-        """on (default): the decode kernel ends only when all peers' rows have landed; off: it only
-        signals and `wait` enqueues a separate wait kernel."""
+        """off (default): the decode kernel only signals and `wait` / `wait_epoch` enqueue a separate wait
+        kernel, so the next step's decode can run ahead of the wait; on: the decode kernel itself ends only
+        when all peers' rows have landed."""
         self._lib.check(self._lib.lib().pd_gather_set_wait_in_kernel(self._h, int(bool(on))))
 
     def wait(self, stream=0):
@@ -169,6 +170,10 @@ class GatherGroup:
     def epoch(self):
         return self._lib.lib().pd_gather_epoch(self._h)
 
+    def reset(self, stream=0):
+        """After a KernelTimeout: clear the grid's arrival counter."""
+        self._lib.check(self._lib.lib().pd_gather_reset(self._h, stream))
+
     def buffer_ptr(self, which=-1):
-        """Device pointer of the local gathered buffer (which = 0/1, -1 = the one the last decode filled)."""
+        """Device pointer of the local gathered buffer (which = step mod 4, -1 = the one the last decode filled)."""
         return self._lib.lib().pd_gather_buffer(self._h, which)

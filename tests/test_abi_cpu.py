@@ -130,13 +130,13 @@ def test_cache_config_errors_need_no_gpu(pa):
                                                max_pages_per_slot=2))
 
 
-def test_kernel_variant_knob(pa):
-    v0 = pa.kernel_variant()
-    with pytest.raises(pa.InvalidArgument):
-        pa.set_kernel_variant(99)
-    pa.set_kernel_variant(1)
-    assert pa.tile_tokens(pa.KVDtype.FP16, 128, 4) == 128
-    pa.set_kernel_variant(v0)
+def test_every_exported_entry_point_is_declared():
+    """Nothing is exported that the header does not declare (an undeclared export is an untested one)."""
+    import subprocess
+    from paged_attention_b200 import _lib
+    out = subprocess.check_output(["nm", "-D", "--defined-only", _lib.LIB_PATH], text=True)
+    exported = {line.split()[-1] for line in out.splitlines() if " T " in line and line.split()[-1].startswith("pd_")}
+    assert exported == set(declared_symbols()), exported ^ set(declared_symbols())
 
 
 def test_product_does_not_reach_for_the_oracle():

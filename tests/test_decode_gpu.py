@@ -238,19 +238,6 @@ def test_fp8_cache_against_fp16_cache(torch_cuda, pa):
     assert 1e-3 < rel < 6e-2
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
-@pytest.mark.parametrize("dtype", [FP16, FP8])
-def test_kernel_variants(variant, dtype, torch_cuda, pa):
-    v0 = pa.kernel_variant()
-    try:
-        pa.set_kernel_variant(variant)
-        for case in (Case(dtype, 32, 8, 16, [1, 17, 129, 1000, 4099]), Case(dtype, 8, 1, 8, [3000], num_ctas=50)):
-            err, *_ = run_case(case, torch_cuda, pa, check_bytes=False)
-            assert err < TOL
-    finally:
-        pa.set_kernel_variant(v0)
-
-
 def test_garbage_past_the_end_of_a_page_is_ignored(torch_cuda, pa):
     # a caller-owned pool that was never cleared: NaN bytes beyond the last token of a sequence
     # (and in unused pages) must not reach the output
