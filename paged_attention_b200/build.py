@@ -6,7 +6,7 @@ The library is the product: there is no fallback path, importing the package
 without it raises.
 
 Tuning builds: extra nvcc flags come from the environment variable PD_B200_NVCC_FLAGS
-(e.g. -DPD_B200_FP8_CONFIG=4,2,2,3 for another CTA shape of the e4m3 kernel) and
+(e.g. -DPD_B200_FP8_SHAPE=4222 for another CTA shape of the e4m3 kernel) and
 `-o PATH` writes the library somewhere else; PD_B200_LIB points the package at it.
 """
 import os

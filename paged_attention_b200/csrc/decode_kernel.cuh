@@ -128,7 +128,7 @@ struct Config {
     static constexpr int STAGES          = STAGES_;
     static constexpr int MIN_CTAS        = MIN_CTAS_;
     static constexpr int HEADS           = HEADS_;             // kv heads per tile
-    static_assert(HEADS_ == 1 || (HEADS_ == WARPS_ && GROUPS_PER_WARP_ == 1), "head-fused: one warp per kv head");
+    static_assert(HEADS_ == 1 || (HEADS_ == WARPS_ && GROUPS_PER_WARP_ <= 2), "head-fused: one warp per kv head, one unit per tile");
 };
 
 template<typename KV, int GROUP, typename C>
@@ -158,7 +158,8 @@ struct Shape {
     static constexpr int OUT_STAGE_BYTES  = HEADS > 1 ? C::WARPS * GROUP * HEAD_DIM * 2 : 0;
     // +1024: the pipeline is aligned to the 128B-swizzle period by hand
     static constexpr int SMEM_BYTES  = 1024 + OUT_STAGE_OFFSET + OUT_STAGE_BYTES;
-    static_assert(sizeof(KV) == 2 || (HEADS == 1 && C::GROUPS_PER_WARP % 2 == 0), "e4m3 cache: a warp works on 32-token units");
+    static_assert(sizeof(KV) == 2 ? (HEADS == 1 || C::GROUPS_PER_WARP == 1) : C::GROUPS_PER_WARP % 2 == 0,
+                  "a warp works on 16-token units of an fp16 cache, 32-token units of an e4m3 cache");
     static_assert(GROUP >= 1 && GROUP <= 8, "a KV group fills the 8 columns of one MMA");
 };
 
@@ -260,11 +261,6 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t fp8x2_to_half2(uint32_t two_bytes) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 // Byte offset, inside one K or V tile, of the 128-byte shared-memory row that
 // holds token `t` (0..TILE-1), panel `h` (fp16: dims 64h..64h+63; fp8: h = 0).
 // A tile is a run of boxes of 2^btl tokens; a box is [panel][token][128 B].
@@ -375,118 +371,49 @@ __device__ __forceinline__ bool process_group_f16(const uint32_t k_tile, const u
 
 // ---- e4m3 cache, one 32-token group ------------------------------------------------------------------
 //
-// The cache bytes go to the tensor cores as they are (mma.m16n8k32 on e4m3 operands): nothing is widened
-// in registers.  What meets them has to be e4m3 too, so the fp16 query rows are split, exactly, into three
-// e4m3 terms (q * 2^e = q1 + q2 + q3 with a per-head power of two that brings the row's largest element
-// just under 256; each term takes the next four significant bits, eleven in all), and the softmax weights,
-// which the fp16 path rounds to fp16 before the PV product, are rounded to fp16 likewise and then split the
-// same way (256 p = p1 + p2 + p3).  Three MMAs per operand tile instead of one, no conversion per cache byte:
-// 48 tensor and about 100 other instructions per 32 tokens, against about 660 with the bytes widened to
-// fp16 first, which had made the fp8 layer issue-bound.
-//
-// Fragment bookkeeping.  K tile as the A operand (tokens x 32 dims per k-step): lane (g, qd) reads the 16-byte
-// chunks 2qd and 2qd+1 of its two token rows; word ks of chunk 2qd is a0/a1 of k-step ks (dims 32qd + 4ks + j),
-// word ks of chunk 2qd+1 is a2/a3 (dims 32qd + 16 + 4ks + j); the query fragments use the same dims.
-// MMA row r of a 16-token half holds token tau(r) = r (r < 8), 8 + ((r + 4) & 7) (r >= 8): any assignment
-// would do for QK, this one makes the 16 rows that one transposed 8-bit ldmatrix of V touches fall into
-// different bank groups under the 128-byte swizzle.  V tile as the A operand of O^T += V^T P^T (16 dims x 32
-// tokens): ldmatrix.m16n16.x2.trans.b8 over the 16-byte chunk `mt` of 32 token rows yields a0..a3 directly;
-// matrix row k of a half is token tau(2(k >> 2) + (k >> 1 & 1) + 8(k & 1)), which is where movmatrix puts the
-// weight of that token in P^T's B fragment (bytes paired as (row r, row r + 8) per head before the transpose).
-//
-// m_run carries the running maximum minus 8, so that the weights are 256 exp2(x - max): up to 256 instead
-// of 1, which keeps three e4m3 terms of small weights out of the subnormal range.  l_run, the accumulators
-// and the LSE m_run + log2(l_run) are then those of a softmax taken relative to (max - 8): the same
-// quantities every later step (cross-warp combine, partials, merge) expects.
+// The cache bytes are widened to fp16 in registers (cvt.f16x2.e4m3x2, exact) and meet the fp16 query rows
+// and the fp16-rounded softmax weights in the same mma.m16n8k16 as the fp16 cache.  (mma.sync on e4m3
+// operands is not a tensor-core instruction of sm_100a: it compiles, but ncu counts 18 issued instructions
+// per mma - widening of both operands, two fp16 MMAs, four adds - so feeding the bytes to it directly, with
+// queries and weights split into three e4m3 terms each, cost 870 instructions per 32 tokens and was slower.)
+// What keeps the instruction count per byte down, since an fp8 layer has half the bytes per token and the
+// same work per token as an fp16 one:
+//  * a warp's unit is 32 tokens: one round of maxima, shuffles and exponentials per 32 tokens;
+//  * K as the A operand: lane (g, qd) reads the 16-byte chunks 2qd, 2qd+1 of its token rows; each 4-byte word
+//    widens into the two halves of a k-step's fragment (dims d, d+1 | d+2, d+3; the query fragments are loaded
+//    in the same dim order, which a dot product does not see);
+//  * V as the A operand of O^T += V^T P^T: ldmatrix.m16n16.x2.trans.b8 over chunk `mt` of the 32 token rows
+//    delivers, per lane, dim g (and g + 8) of four tokens per half as one register each; widened, they are
+//    the fragments of that dim tile for both 16-token halves, with no byte shuffling at all;
+//  * the accumulators are rescaled only when some running maximum moved (rare after the first tiles).
+// MMA row r of a 16-token half holds token tau16(r): any assignment would do, this one makes the 16 rows that
+// one transposed ldmatrix touches fall into different bank groups under the 128-byte swizzle.
 __device__ __forceinline__ int tau16(int r) { return r < 8 ? r : 8 + ((r + 4) & 7); }
 
-// Four floats -> the four nearest e4m3 bytes (byte j from v[j]); v is left holding the residuals.
-__device__ __forceinline__ uint32_t split_e4m3x4(float (&v)[4]) {
-    uint16_t lo, hi;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(v[1]), "f"(v[0]));
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(v[3]), "f"(v[2]));
-    uint32_t blo, bhi;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(blo) : "h"(lo));
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(bhi) : "h"(hi));
-    const float2 flo = __half22float2(*reinterpret_cast<const __half2*>(&blo));
-    const float2 fhi = __half22float2(*reinterpret_cast<const __half2*>(&bhi));
-    v[0] -= flo.x; v[1] -= flo.y; v[2] -= fhi.x; v[3] -= fhi.y;
-    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+__device__ __forceinline__ uint32_t widen_lo(uint32_t w) {      // bytes 0, 1 -> f16x2
+    uint32_t r;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(r) : "r"(w));
+    return r;
 }
-// half2 -> two e4m3 bytes (low half -> low byte); h is left holding the residual (exact in fp16).
-__device__ __forceinline__ uint32_t split_e4m3x2(uint32_t& h) {
-    uint16_t e;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(e) : "r"(h));
-    uint32_t back;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(back) : "h"(e));
-    asm("sub.rn.f16x2 %0, %0, %1;" : "+r"(h) : "r"(back));
-    return e;
+__device__ __forceinline__ uint32_t widen_hi(uint32_t w) {      // bytes 2, 3 -> f16x2
+    uint32_t r;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(r) : "r"(w));
+    return r;
 }
-__device__ __forceinline__ uint32_t to_e4m3x2(uint32_t h) {
-    uint16_t e;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(e) : "r"(h));
-    return e;
-}
-// D(16x8) += A(16x32, row) * B(32x8, col), e4m3 in, fp32 accumulate.
-__device__ __forceinline__ void mma_16832_e4m3(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
-                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// 16 dims x 32 tokens of a byte tile, transposed into the A fragment of mma.m16n8k32: lanes 0..15 give the
-// addresses of the 16-byte chunks of matrix rows (tokens) 0..15, lanes 16..31 of rows 16..31.
+// 16 dims x 32 tokens of a byte tile, transposed: lanes 0..15 give the addresses of the 16-byte chunks of
+// matrix rows (tokens) 0..15, lanes 16..31 of rows 16..31.  Lane (g, qd) receives r0: dim g of rows 4qd..4qd+3,
+// r1: dim g + 8 of the same rows, r2, r3: the same for rows 16 + 4qd...
 __device__ __forceinline__ void ldmatrix_b8_x2_trans(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// The query row of head g (fp16, 128 dims at `qrow` in shared memory) as three sets of B fragments:
-// qb[4 * term + ks] for k-step ks.  Returns e with q * 2^e split; dead rows (live = false) give zeros.
-__device__ __forceinline__ int load_q_e4m3(uint32_t (&qb)[12][2], const uint32_t qrow, const bool live, const int lane)
-{
-    const int qd = lane & 3;
-    uint32_t raw[16];                          // dims 32qd .. 32qd+31 of this head, two per word
-#pragma unroll
-    for (int c = 0; c < 4; c++) {
-        const uint4 w = lds128(qrow + (32 * qd + 8 * c) * 2);
-        raw[4 * c] = live ? w.x : 0u; raw[4 * c + 1] = live ? w.y : 0u;
-        raw[4 * c + 2] = live ? w.z : 0u; raw[4 * c + 3] = live ? w.w : 0u;
-    }
-    __half2 mx2 = __float2half2_rn(0.f);
-#pragma unroll
-    for (int i = 0; i < 16; i++) mx2 = __hmax2(mx2, __habs2(*reinterpret_cast<const __half2*>(&raw[i])));
-    float mx = fmaxf(__low2float(mx2), __high2float(mx2));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    // mx in [2^(E-127), 2^(E-126)): scaled by 2^(134-E) it lies in [128, 256)
-    const int E = static_cast<int>((__float_as_uint(mx) >> 23) & 0xffu);
-    const int e = (E >= 8 && E < 255) ? 134 - E : 0;
-    const float up = __uint_as_float(static_cast<uint32_t>(e + 127) << 23);
-#pragma unroll
-    for (int ks = 0; ks < 4; ks++) {
-#pragma unroll
-        for (int half = 0; half < 2; half++) {          // b0: dims 4ks.., b1: dims 16 + 4ks.. (of the lane's 32)
-            const int w = 8 * half + 2 * ks;
-            const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&raw[w]));
-            const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&raw[w + 1]));
-            float v[4] = {f01.x * up, f01.y * up, f23.x * up, f23.y * up};
-            qb[ks][half]     = split_e4m3x4(v);
-            qb[4 + ks][half] = split_e4m3x4(v);
-            qb[8 + ks][half] = split_e4m3x4(v);
-        }
-    }
-    return e;
-}
-
 // grp_row: first token of the group inside the tile; grp_valid (1..32+): how many of its tokens exist.
-// col_scale: softmax scale (base 2, with the K scale and 2^-e of the query split) of heads 2qd, 2qd+1.
 template<typename Rows>
 __device__ __forceinline__ bool process_group_e4m3(const uint32_t k_tile, const uint32_t v_tile, const Rows rows,
-                                                   const int grp_row, const int grp_valid, const uint32_t (&qb)[12][2],
+                                                   const int grp_row, const int grp_valid, const uint32_t (&qb)[8][2],
                                                    float (&acc)[8][4], float (&m_run)[2], float (&l_run)[2],
-                                                   const float (&col_scale)[2], const int lane)
+                                                   const float qk_scale, const int lane)
 {
     const int g = lane >> 2, qd = lane & 3;
     bool wrote = false;
@@ -500,26 +427,28 @@ __device__ __forceinline__ bool process_group_e4m3(const uint32_t k_tile, const 
         __syncwarp();
     }
 
-    // ---- 1. S^T = K Q^T for both 16-token halves; one accumulator per query term.
+    // ---- 1. S^T = K Q^T for both 16-token halves, two interleaved accumulators each.
     const int tok_lo = g, tok_hi = tau16(g + 8);      // tokens of MMA rows g, g + 8 within a half
     float x[2][4];
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
         const uint32_t r0 = rows(grp_row + 16 * hh + tok_lo, 0), r1 = rows(grp_row + 16 * hh + tok_hi, 0);
-        const uint4 a02 = lds128(k_tile + swz(r0, 2 * qd)), a02b = lds128(k_tile + swz(r0, 2 * qd + 1));
-        const uint4 a13 = lds128(k_tile + swz(r1, 2 * qd)), a13b = lds128(k_tile + swz(r1, 2 * qd + 1));
-        const uint32_t w0[4] = {a02.x, a02.y, a02.z, a02.w}, w2[4] = {a02b.x, a02b.y, a02b.z, a02b.w};
-        const uint32_t w1[4] = {a13.x, a13.y, a13.z, a13.w}, w3[4] = {a13b.x, a13b.y, a13b.z, a13b.w};
-        float s[3][4];
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int t = 0; t < 3; t++) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+        for (int j = 0; j < 2; j++) {
+            const uint4 lo = lds128(k_tile + swz(r0, 2 * qd + j));
+            const uint4 hi = lds128(k_tile + swz(r1, 2 * qd + j));
+            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++)
+            for (int m = 0; m < 4; m++) {
+                const uint32_t a[4] = {widen_lo(wl[m]), widen_lo(wh[m]), widen_hi(wl[m]), widen_hi(wh[m])};
+                const int ks = 4 * j + m;
+                if (m & 1) mma_16816(s1, a, qb[ks][0], qb[ks][1]);
+                else       mma_16816(s0, a, qb[ks][0], qb[ks][1]);
+            }
+        }
 #pragma unroll
-            for (int t = 0; t < 3; t++)
-                mma_16832_e4m3(s[t], w0[ks], w1[ks], w2[ks], w3[ks], qb[4 * t + ks][0], qb[4 * t + ks][1]);
-#pragma unroll
-        for (int i = 0; i < 4; i++) x[hh][i] = ((s[2][i] + s[1][i]) + s[0][i]) * col_scale[i & 1];
+        for (int i = 0; i < 4; i++) x[hh][i] = (s0[i] + s1[i]) * qk_scale;
         if (grp_valid < 32) {
             if (16 * hh + tok_lo >= grp_valid) { x[hh][0] = -INFINITY; x[hh][1] = -INFINITY; }
             if (16 * hh + tok_hi >= grp_valid) { x[hh][2] = -INFINITY; x[hh][3] = -INFINITY; }
@@ -537,7 +466,7 @@ __device__ __forceinline__ bool process_group_e4m3(const uint32_t k_tile, const 
     float alpha[2];
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-        const float m_new = fmaxf(m_run[h], mx[h] - 8.f);
+        const float m_new = fmaxf(m_run[h], mx[h]);
         alpha[h] = exp2f(m_run[h] - m_new);
         m_run[h] = m_new;
     }
@@ -557,32 +486,27 @@ __device__ __forceinline__ bool process_group_e4m3(const uint32_t k_tile, const 
         }
     }
 
-    // ---- 3. the weights as three e4m3 terms each, transposed into B fragments.
-    uint32_t pb[3][2];
+    // ---- 3. O^T += V^T P^T.  P^T's B fragments = transposed 8x8 blocks of the weights (MMA rows 0..7, 8..15).
+    uint32_t pb[2][2];
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
-        uint32_t h02 = pack_half2(pr[hh][0], pr[hh][2]);     // head 2qd:   rows g, g + 8
-        uint32_t h13 = pack_half2(pr[hh][1], pr[hh][3]);     // head 2qd+1
-        const uint32_t t0 = split_e4m3x2(h02) | (split_e4m3x2(h13) << 16);
-        const uint32_t t1 = split_e4m3x2(h02) | (split_e4m3x2(h13) << 16);
-        const uint32_t t2 = to_e4m3x2(h02) | (to_e4m3x2(h13) << 16);
-        pb[0][hh] = movmatrix_trans(t0);
-        pb[1][hh] = movmatrix_trans(t1);
-        pb[2][hh] = movmatrix_trans(t2);
+        pb[hh][0] = movmatrix_trans(pack_half2(pr[hh][0], pr[hh][1]));
+        pb[hh][1] = movmatrix_trans(pack_half2(pr[hh][2], pr[hh][3]));
     }
-
-    // ---- 4. O^T += V^T P^T.
     {
-        const int k = lane & 15;
-        const int t = grp_row + 16 * (lane >> 4) + tau16(2 * (k >> 2) + ((k >> 1) & 1) + 8 * (k & 1));
+        // matrix row i of a half = MMA row (k index) 2(i >> 2) + (i & 1) + 8(i >> 1 & 1): the widened low half of a
+        // register is then k = 2qd, 2qd+1 (a0 / a1), the high half k = 2qd+8, 2qd+9 (a2 / a3)
+        const int i = lane & 15;
+        const int t = grp_row + 16 * (lane >> 4) + tau16(2 * (i >> 2) + (i & 1) + 8 * ((i >> 1) & 1));
         const uint32_t r = rows(t, 0);
 #pragma unroll
         for (int mt = 0; mt < 8; mt++) {
-            uint32_t a[4];
-            ldmatrix_b8_x2_trans(a, v_tile + swz(r, mt));
-            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[0][0], pb[0][1]);
-            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[1][0], pb[1][1]);
-            mma_16832_e4m3(acc[mt], a[0], a[1], a[2], a[3], pb[2][0], pb[2][1]);
+            uint32_t v[4];
+            ldmatrix_b8_x2_trans(v, v_tile + swz(r, mt));
+            const uint32_t a0[4] = {widen_lo(v[0]), widen_lo(v[1]), widen_hi(v[0]), widen_hi(v[1])};
+            const uint32_t a1[4] = {widen_lo(v[2]), widen_lo(v[3]), widen_hi(v[2]), widen_hi(v[3])};
+            mma_16816(acc[mt], a0, pb[0][0], pb[0][1]);
+            mma_16816(acc[mt], a1, pb[1][0], pb[1][1]);
         }
     }
     return wrote;
@@ -895,8 +819,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
 
     float acc[8][4];
     float m_run[2], l_run[2];
-    uint32_t qb[FP8 ? 12 : 8][2];   // Q^T B-fragments: fp16, 8 k-steps; e4m3, three terms of 4 k-steps
-    float col_scale[2] = {qk_scale, qk_scale};   // e4m3: qk_scale / 2^e of heads 2qd, 2qd+1 (e: the query split's exponent)
+    uint32_t qb[8][2];          // Q^T B-fragments for the 8 k-steps
 
     unsigned tiles_done = 0;
     int c_stage = 0;            // stage of the next tile to consume and the parity of its round
@@ -928,10 +851,17 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 + (static_cast<size_t>(sg.x) * p.num_q_heads + warp * GROUP + (live ? g : 0)) * HEAD_DIM;
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-                const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd));
-                const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd));
-                qb[ks][0] = live ? lo : 0u;
-                qb[ks][1] = live ? hi : 0u;
+                if constexpr (FP8) {
+                    const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
+                    const uint2 v = __ldg(reinterpret_cast<const uint2*>(qrow + db));
+                    qb[ks][0] = live ? v.x : 0u;
+                    qb[ks][1] = live ? v.y : 0u;
+                } else {
+                    const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * qd));
+                    const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * qd));
+                    qb[ks][0] = live ? lo : 0u;
+                    qb[ks][1] = live ? hi : 0u;
+                }
             }
         }
 #pragma unroll
@@ -948,15 +878,15 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 need_q = false;
                 const bool live = g < GROUP;
                 const uint32_t qrow = q_slots + stage * S::Q_SLOT_BYTES + (live ? g : 0) * (HEAD_DIM * 2);
-                if constexpr (FP8) {
-                    const int e = load_q_e4m3(qb, qrow, live, lane);
-                    // this lane's score columns are heads 2qd, 2qd+1, whose exponents live in lanes with g = 2qd, 2qd+1
-                    const int e0 = __shfl_sync(0xffffffffu, e, 8 * qd), e1 = __shfl_sync(0xffffffffu, e, 8 * qd + 4);
-                    col_scale[0] = qk_scale * __uint_as_float(static_cast<uint32_t>(127 - e0) << 23);
-                    col_scale[1] = qk_scale * __uint_as_float(static_cast<uint32_t>(127 - e1) << 23);
-                } else {
 #pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
+                for (int ks = 0; ks < 8; ks++) {
+                    if constexpr (FP8) {
+                        // k-slots {2qd, 2qd+1 | 2qd+8, 2qd+9} of k-step ks are dims db..db+3: one 4-byte word of K
+                        const int db = (2 * qd + (ks >> 2)) * 16 + (ks & 3) * 4;
+                        const uint2 v = lds64(qrow + db * 2);
+                        qb[ks][0] = live ? v.x : 0u;
+                        qb[ks][1] = live ? v.y : 0u;
+                    } else {
                         const uint32_t lo = lds32(qrow + (ks * 16 + 2 * qd) * 2);
                         const uint32_t hi = lds32(qrow + (ks * 16 + 8 + 2 * qd) * 2);
                         qb[ks][0] = live ? lo : 0u;
@@ -979,7 +909,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 const int box_head = S::HEADS > 1 ? warp : 0;
                 auto rows = [&](int t, int panel) { return row_offset<KV, S::HEADS>(t, panel, btl, box_head); };
                 if constexpr (FP8)
-                    wrote |= process_group_e4m3(k_tile, v_tile, rows, grp_row, grp_valid, qb, acc, m_run, l_run, col_scale, lane);
+                    wrote |= process_group_e4m3(k_tile, v_tile, rows, grp_row, grp_valid, qb, acc, m_run, l_run, qk_scale, lane);
                 else
                     wrote |= process_group_f16(k_tile, v_tile, rows, grp_row, grp_valid, qb, acc, m_run, l_run, qk_scale, lane);
             }

@@ -53,19 +53,21 @@ int set_error(int code, const char* fmt, ...) {
 
 // ---- kernel shapes --------------------------------------------------------------------
 // CTA shape and pipeline depth per cache dtype: Config<consumer warps, 16-token groups per warp per tile,
-// stages, CTAs per SM>.  4 consumer warps + 1 producer warp per CTA.  fp16: 64-token tiles, 3 stages of
-// 32 KB, two CTAs per SM.  Both keep about 96..128 KB of copies in flight per SM, where the measured load
-// rate of the pipeline peaks; more in flight is slower.  The two macros let a tuning build try other shapes
-// (python -m paged_attention_b200.build takes them from the environment variable PD_B200_NVCC_FLAGS).
-#ifndef PD_B200_FP16_CONFIG
-#define PD_B200_FP16_CONFIG 4, 1, 3, 2
+// stages, CTAs per SM>, plus one producer warp per CTA.  fp16: 4 warps, 64-token tiles, 3 stages of 32 KB, two
+// CTAs per SM.  e4m3: 4 warps of two groups (a warp's unit is 32 tokens), 128-token tiles, 3 stages of 32 KB,
+// two CTAs per SM.  The two macros let a tuning build try other shapes (python -m paged_attention_b200.build
+// takes extra compiler flags from the environment variable PD_B200_NVCC_FLAGS).
+#ifndef PD_B200_FP16_SHAPE
+#define PD_B200_FP16_SHAPE 4132
 #endif
-#ifndef PD_B200_FP8_CONFIG
-#define PD_B200_FP8_CONFIG 4, 2, 3, 2
+#ifndef PD_B200_FP8_SHAPE
+#define PD_B200_FP8_SHAPE 4232
 #endif
+// a shape is written as four decimal digits: warps, groups per warp, stages, CTAs per SM
+template<int DIGITS> using ShapeOf = pdk::Config<DIGITS / 1000, DIGITS / 100 % 10, DIGITS / 10 % 10, DIGITS % 10>;
 template<typename KV> struct DefaultConfig;
-template<> struct DefaultConfig<__half>        { using type = pdk::Config<PD_B200_FP16_CONFIG>; };
-template<> struct DefaultConfig<__nv_fp8_e4m3> { using type = pdk::Config<PD_B200_FP8_CONFIG>; };
+template<> struct DefaultConfig<__half>        { using type = ShapeOf<PD_B200_FP16_SHAPE>; };
+template<> struct DefaultConfig<__nv_fp8_e4m3> { using type = ShapeOf<PD_B200_FP8_SHAPE>; };
 
 struct KernelInfo {
     const void* fn;
@@ -134,6 +136,9 @@ const KernelInfo* info_by_group(int group) {
 // DRAM locality), so fp8 keeps the (row, kv head) schedule at three CTAs per SM.
 template<typename KV> struct FusedConfig;
 template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>; };
+// e4m3: a warp's unit is 32 tokens, so a tile is 32 tokens of all 8 kv heads: two 16 KB boxes per pool and tile
+// with 16-token pages, the same 64 KB per stage as the fp16 shape.
+template<> struct FusedConfig<__nv_fp8_e4m3> { using type = pdk::Config<8, 2, 3, 1, 8>; };
 
 template<int GROUP>
 void launch_merge_rows(const pd_params& p, int seg_limit, cudaStream_t stream) {
@@ -151,7 +156,7 @@ KernelInfo make_fused_info() {
 }
 
 template<typename KV>
-const KernelInfo* fused_info(int group) {
+const KernelInfo* fused_info_of(int group) {
     static const KernelInfo t[4] = {make_fused_info<KV, 1>(), make_fused_info<KV, 2>(), make_fused_info<KV, 4>(),
                                     make_fused_info<KV, 8>()};
     switch (group) {
@@ -162,8 +167,13 @@ const KernelInfo* fused_info(int group) {
     }
     return nullptr;
 }
+// The head-fused kernel of a cache dtype (its tile is 16 tokens for fp16, 32 for e4m3); null for other dtypes.
+const KernelInfo* fused_info(int dtype, int group) {
+    if (dtype == PD_FP16) return fused_info_of<__half>(group);
+    if (dtype == PD_FP8_E4M3) return fused_info_of<__nv_fp8_e4m3>(group);
+    return nullptr;
+}
 constexpr int FUSED_HEADS = 8;
-constexpr int FUSED_TILE  = 16;
 int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   // 0 never, 1 where it wins, 2 always
 
 }  // namespace
@@ -603,17 +613,20 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     // pd_make_plan) and the layer has exactly 8 kv heads: rows are the work items, 16 tokens the unit.
     pd_plan* rows_plan = nullptr;
     const KernelInfo* fk = nullptr;
-    const bool layer_known = plan->dtype == PD_FP16 || plan->dtype == -2;   // -2: rebuilt from arrays, dtype checked at decode
+    // -2: rebuilt from arrays, the dtype is only known at decode; such plans get the fp16 kernel's row cut, which
+    // a decode with another dtype ignores (its tile differs)
+    const bool layer_known = plan->dtype == PD_FP16 || plan->dtype == PD_FP8_E4M3 || plan->dtype == -2;
+    const int fused_dtype = plan->dtype == -2 ? PD_FP16 : plan->dtype;
     if (layer_known && plan->num_kv_heads == FUSED_HEADS && plan->batch > 0 &&
         (plan->num_q_heads == 0 || plan->num_q_heads / plan->num_kv_heads == group) && head_dim == 128) {
-        fk = fused_info<__half>(group);
+        fk = fused_info(fused_dtype, group);
         int grid = plan->forced_ctas;
         if (fk && grid <= 0) grid = fused_wave(fk);
         // a plan rebuilt from a caller's arrays does not say whether its grid was asked for; a grid smaller
         // than one CTA per SM is taken as asked for (sharing the GPU, a sweep) and kept
         if (fk && plan->dtype == -2 && plan->num_ctas > 0 && plan->num_ctas < grid) grid = plan->num_ctas;
         if (!fk || grid <= 0 ||
-            build_plan(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
+            build_plan(fk->tile, plan->seq_lens.data(), plan->batch, 1, 1, grid, &rows_plan) != PD_OK)
             rows_plan = nullptr;
     }
     // Adaptive cut: the schedule that will run (head-fused where it wins, else the caller's) is cut again in
@@ -630,7 +643,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
             if (t) stats_fused = t->slots;
             if (t && !weights.empty()) {
                 pd_plan* w = nullptr;
-                if (build_plan_weighted(FUSED_TILE, plan->seq_lens.data(), plan->batch, 1, weights, &w) == PD_OK) {
+                if (build_plan_weighted(fk->tile, plan->seq_lens.data(), plan->batch, 1, weights, &w) == PD_OK) {
                     delete rows_plan;
                     rows_plan = w;
                 }
@@ -809,8 +822,8 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
     // by its own piece count who merges it, see MERGE_HYBRID).
     const KernelInfo* fk = nullptr;
     int fgrid = 0;
-    if (dtype == PD_FP16 && num_kv_heads == FUSED_HEADS && head_dim == 128 && g_head_fused != 0) {
-        fk = fused_info<__half>(group);
+    if (num_kv_heads == FUSED_HEADS && head_dim == 128 && g_head_fused != 0) {
+        fk = fused_info(dtype, group);
         fgrid = num_ctas > 0 ? num_ctas : fused_wave(fk);
         if (!fk || fgrid <= 0 || (g_head_fused == 1 && batch * 3 < fgrid)) { fk = nullptr; fgrid = 0; }
     }
@@ -897,7 +910,7 @@ int pd_device_plan_build(pd_device_plan* dp, int dtype, const int* d_seq_lens, c
         f.partial_out = dp->partial + std_need;
         pdk::PlanJob fj{};
         fj.seq_lens = d_seq_lens; fj.slot_ids = d_slot_ids;
-        fj.batch = batch; fj.num_kv_heads = 1; fj.tile = FUSED_TILE; fj.grid = fgrid;   // work items are rows
+        fj.batch = batch; fj.num_kv_heads = 1; fj.tile = fk->tile; fj.grid = fgrid;   // work items are rows
         fj.lse_per_segment = num_q_heads; fj.num_counters = static_cast<int>(items);
         fj.segments = reinterpret_cast<int4*>(fa);
         fj.cta_seg_begin = const_cast<int*>(f.cta_seg_begin);
@@ -1009,9 +1022,9 @@ Selection select_schedule(int dtype, const pd_params* p, const KernelInfo* k, bo
     }
     const int group = p->num_q_heads / p->num_kv_heads;
     auto matches = [&](const pd_device_plan::Fused& f) {
-        return f.valid && (f.dtype == dtype || f.dtype == -2) && f.batch == p->batch && f.group == group;
+        return f.valid && (f.dtype == dtype || (f.dtype == -2 && dtype == PD_FP16)) && f.batch == p->batch && f.group == group;
     };
-    const KernelInfo* fk = dtype == PD_FP16 && p->num_kv_heads == FUSED_HEADS ? fused_info<__half>(group) : nullptr;
+    const KernelInfo* fk = p->num_kv_heads == FUSED_HEADS ? fused_info(dtype, group) : nullptr;
     // Head-fused, mode 1: not where rows would be spread over more than 4 CTAs each.
     const bool use_fused = fk && g_head_fused && matches(alt.fused) &&
                            (g_head_fused == 2 || alt.fused.needs_merge != pdk::MERGE_SEPARATE);

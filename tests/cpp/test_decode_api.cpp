@@ -201,6 +201,39 @@ int main() {
         for (half x : out) CHECK(std::fabs(__half2float(x) - 0.25f) < 1e-3f);   // all values equal -> output is that value
         cudaFree(d); cudaFree(dq); cudaFree(dout);
     }
+    // A caller that asks for a small grid (to share the GPU with another stream, or to sweep CTA counts) gets
+    // no more CTAs than it asked for, also where the library swaps in its own schedule of the same step
+    // (fp16 layers with 8 kv heads run a row-wise schedule on a grid of their own).
+    {
+        const int B = 3, hq = 32, hkv = 8, D = 128, page = 16, L = 2000;
+        PagedKVCache::Config cfg{};
+        cfg.num_pages = B * 125; cfg.page_size = page; cfg.num_kv_heads = hkv; cfg.head_dim = D; cfg.max_slots = B; cfg.max_pages_per_slot = 125;
+        PagedKVCache cache(cfg);
+        std::vector<half> kv(static_cast<size_t>(L) * hkv * D, __float2half(-0.75f));
+        half* d = upload(kv);
+        for (int b = 0; b < B; b++) CHECK(cache.append(cache.admit(), d, d, L));
+        std::vector<half> q(static_cast<size_t>(B) * hq * D, __float2half(0.125f));
+        half* dq = upload(q);
+        half* dout = nullptr;
+        cudaMalloc(&dout, sizeof(half) * q.size());
+        for (int asked : {9, 40}) {
+            decode::DecodePlan plan = decode::make_plan(KVDtype::FP16, {L, L, L}, hq, hkv, D, asked);
+            decode::DevicePlan dp;
+            dp.upload(plan, hq / hkv, D);
+            decode::DecodeParams p = cache.params();
+            p.q = dq; p.out = dout; p.batch = B; p.num_q_heads = hq;
+            dp.bind(p);
+            int info[8] = {};
+            CHECK(pd_describe_launch(PD_FP16, decode::as_pd(p), info) == PD_OK);
+            CHECK(info[1] > 0 && info[1] <= asked);
+            decode::paged_decode(KVDtype::FP16, p);
+            cudaDeviceSynchronize();
+            std::vector<half> out(q.size());
+            cudaMemcpy(out.data(), dout, sizeof(half) * out.size(), cudaMemcpyDeviceToHost);
+            for (half x : out) CHECK(std::fabs(__half2float(x) + 0.75f) < 1e-3f);
+        }
+        cudaFree(d); cudaFree(dq); cudaFree(dout);
+    }
     // The legacy interfaces with the engine behind them: backend-vs-CPU parity on seeded uniform(-1,1)
     // inputs (tests/test_helpers.hpp:10-19 of the reference, at fp16-storage tolerance) and the pool
     // semantics its pool tests pin (tests/test_paged_pool.cpp:25-77,135-156; tests/test_contiguous_pool.cpp:34-65).

@@ -1,4 +1,4 @@
-"""The two schedules of the fp16 decode kernel on layers with 8 kv heads.
+"""The two schedules of the decode kernel on layers with 8 kv heads (both cache dtypes).
 
 Plans made by the planner run, by default, with tiles of 16 tokens x all 8 kv heads (one consumer warp
 per kv head, work cut by rows) where that wins (rows cut in at most 4 pieces); otherwise, and with the
@@ -13,7 +13,7 @@ from common import TOL, Case, raw_decode, run_case, seeded_kv
 
 pytestmark = pytest.mark.gpu
 
-FP16 = 0
+FP16, FP8 = 0, 1
 
 
 @pytest.fixture
@@ -47,17 +47,19 @@ def both_schedules(pa):
     (24, [1000, 25], 0),
     (4096, [5000, 4096], 0),
 ])
-def test_fused_and_row_head_schedules_agree(ps, lens, ctas, torch_cuda, pa, both_schedules):
-    case = Case(FP16, 32, 8, ps, lens, num_ctas=ctas, shuffle=9, seed=77)
+@pytest.mark.parametrize("dtype", [FP16, FP8])
+def test_fused_and_row_head_schedules_agree(dtype, ps, lens, ctas, torch_cuda, pa, both_schedules):
+    case = Case(dtype, 32, 8, ps, lens, num_ctas=ctas, shuffle=9, seed=77)
     (e1, o1, want, i1), (e2, o2, _, i2) = both_schedules(lambda: run_case(case, torch_cuda, pa))
     assert e1 <= TOL and e2 <= TOL, (e1, e2)
     assert float(np.abs(o1 - o2).max()) <= TOL
     assert i1 == i2, "the plan a caller sees does not depend on the schedule"
 
 
+@pytest.mark.parametrize("dtype", [FP16, FP8])
 @pytest.mark.parametrize("hq", [8, 16, 32, 64])
-def test_group_sizes_on_eight_kv_heads(hq, torch_cuda, pa, both_schedules):
-    case = Case(FP16, hq, 8, 16, [2049, 300, 16], shuffle=3, seed=5)
+def test_group_sizes_on_eight_kv_heads(dtype, hq, torch_cuda, pa, both_schedules):
+    case = Case(dtype, hq, 8, 16, [2049, 300, 16], shuffle=3, seed=5)
     (e1, o1, _, _), (e2, o2, _, _) = both_schedules(lambda: run_case(case, torch_cuda, pa))
     assert e1 <= TOL and e2 <= TOL, (e1, e2)
     assert float(np.abs(o1 - o2).max()) <= TOL
@@ -169,13 +171,14 @@ def test_plan_rebuilt_from_arrays_gets_both_schedules(torch_cuda, pa):
     cache.close()
 
 
+@pytest.mark.parametrize("dtype", [FP16, FP8])
 @pytest.mark.parametrize("hq", [8, 16])
 @pytest.mark.parametrize("ctas", [0, 37, 50, 99])
-def test_small_groups_with_split_rows(hq, ctas, torch_cuda, pa, both_schedules):
+def test_small_groups_with_split_rows(dtype, hq, ctas, torch_cuda, pa, both_schedules):
     """Groups of 1 and 2 query heads per kv head with rows cut across CTAs: the second schedule's partial
     rows start wherever the first schedule's workspace ends, and the merges read them 16 bytes at a time,
     so every region of the workspace has to start on a 16-byte boundary for any segment count."""
-    case = Case(FP16, hq, 8, 16, [3000] * 21 + [17], num_ctas=ctas, shuffle=4, seed=15)
+    case = Case(dtype, hq, 8, 16, [3000] * 21 + [17], num_ctas=ctas, shuffle=4, seed=15)
     (e1, o1, _, i1), (e2, o2, _, _) = both_schedules(lambda: run_case(case, torch_cuda, pa))
     assert e1 <= TOL and e2 <= TOL, (e1, e2)
     assert float(np.abs(o1 - o2).max()) <= TOL
