@@ -352,14 +352,14 @@ class Gather:
             self.views = [torch.as_tensor(_Dev(self.gg.buffer_ptr(i), self.full_bytes), device="cuda") for i in range(4)]
             self.share = self.full_bytes // world      # each rank returns its 1/world of the gathered result to the host
             self.full_host = torch.empty(self.share, dtype=torch.uint8).pin_memory()
-        self.first_epoch = None
 
-    def decode(self):
-        """One layer with its rows stored into every rank's buffer; does not wait for the peers' rows."""
+    def decode(self, sync=False):
+        """One layer with its rows stored into every rank's buffer.  sync: the kernel launched behind the decode
+        also waits for the peers' rows (the step is complete when it has run); else `wait` does, later."""
         ly = self.layer
         if self.mode == "peer":
             self.gg.decode(self.pa.KVDtype(ly.dtype), ly.params, self.heads_total, self.head_off, self.row_off, ly.stream,
-                           ly.cfg.num_pages)
+                           ly.cfg.num_pages, sync=sync)
         else:
             ly.decode()
             self.dist.all_gather_into_tensor(self.gathered, ly.out)
@@ -383,8 +383,7 @@ class Gather:
         """After the timed region: this rank's gathered buffer against an NCCL all-gather of the ranks' local
         outputs of the same plan (bit for bit), and two of this rank's rows against the CPU oracle."""
         torch, dist, ly = self.torch, self.dist, self.layer
-        self.decode()
-        self.wait()
+        self.decode(sync=True)
         torch.cuda.synchronize()
         got = self.last_view().clone()
         ly.out.zero_()
@@ -476,22 +475,12 @@ def our_arm(args, wl):
     def measure(layer, gather, steps, warmup, settle_to=24):
         """The step protocol for one layer (+ gather).  Returns a dict of per-step milliseconds (max over ranks)."""
         if gather is None:
-            step, finish = layer.decode, None
-            strict = None
+            step = layer.decode
         else:
-            # Pipelined by one step: step e's decode is launched before the wait for step e-1's rows, so the wait
-            # overlaps the decode; the last step's own rows are waited for inside its events.
+            # a step is complete when every rank's rows are in this rank's buffer: decode, then ONE dependent
+            # kernel that announces this rank's rows and waits for the others'
             def step():
-                gather.decode()
-                if gather.first_epoch is not None and gather.mode == "peer" and gather.gg.epoch > gather.first_epoch:
-                    gather.wait(back=1)
-
-            def finish():
-                gather.wait()
-
-            def strict():
-                gather.decode()
-                gather.wait()
+                gather.decode(sync=True)
         # W warm-up steps as asked (at least 3), preceded by as many settling steps as it takes to make
         # `settle_to` untimed steps in all: the adaptive cut folds in one reading per plan and needs about 20
         # to settle, as it would have in any serving loop.  All of them are reported as warm-up.
@@ -499,21 +488,16 @@ def our_arm(args, wl):
         for _ in range(untimed):
             layer.replan()
             flush()
-            (strict or step)()
+            step()
         barrier()
-        if gather is not None and gather.mode == "peer":
-            gather.first_epoch = gather.gg.epoch
         t0 = time.perf_counter()
-        ms = timed(step, steps, before=layer.replan if args.replan_every_step else None, after_last=finish)
+        ms = timed(step, steps, before=layer.replan if args.replan_every_step else None)
         barrier()
         wall = time.perf_counter() - t0
         res = {"untimed": untimed, "wall": wall, "ms_list": ms}
         res["ms_kernel"] = timed(layer.decode, steps)          # the decode (+ merge) alone, local output
-        if strict:
-            res["ms_strict"] = timed(strict, steps)
-        per = max_over_ranks([sum(ms) / steps, sum(res["ms_kernel"]) / steps, sum(res.get("ms_strict", ms)) / steps,
-                              statistics.median(ms)])
-        res["per_step"], res["per_kernel"], res["per_strict"], res["median"] = per
+        per = max_over_ranks([sum(ms) / steps, sum(res["ms_kernel"]) / steps, statistics.median(ms)])
+        res["per_step"], res["per_kernel"], res["median"] = per
         return res
 
     # ---- the headline workload ------------------------------------------------------------------------------
@@ -539,8 +523,7 @@ def our_arm(args, wl):
             layer.decode()
             layer.out_host.copy_(layer.out, non_blocking=True)
         else:
-            gather.decode()
-            gather.wait()
+            gather.decode(sync=True)
             if gather.mode == "peer":     # the gathered result comes back to the host once, one share per rank
                 buf = gather.views[gather.gg.epoch % 4]
                 gather.full_host.copy_(buf[rank * gather.share:(rank + 1) * gather.share], non_blocking=True)
@@ -568,19 +551,19 @@ def our_arm(args, wl):
     clocks = sampler.stop() if sampler else None
     pa.kernel_status(stream)
 
-    # two layers back to back (no flush between them): strict = decode, wait, decode, wait; pipelined = decode,
-    # decode, wait, wait: the first layer's wait overlaps the second layer's decode
+    # two layers back to back (no flush between them): in order = (decode + announce-and-wait) twice; overlapped =
+    # decode, announce, decode, announce, then the two waits: the first layer's wait overlaps the second decode
     back_to_back = None
     if gather is not None and gather.mode == "peer":
-        def two_strict():
-            gather.decode(); gather.wait(); gather.decode(); gather.wait()
+        def two_in_order():
+            gather.decode(sync=True); gather.decode(sync=True)
 
-        def two_pipelined():
+        def two_overlapped():
             gather.decode(); gather.decode(); gather.wait(back=1); gather.wait()
-        a = max_over_ranks([sum(timed(two_strict, args.steps)) / args.steps])[0]
-        b = max_over_ranks([sum(timed(two_pipelined, args.steps)) / args.steps])[0]
-        back_to_back = {"two_layers_strict_ms": a, "two_layers_pipelined_ms": b,
-                        "note": "events around two consecutive layers; pipelined launches the second decode before waiting for the first layer's rows"}
+        a = max_over_ranks([sum(timed(two_in_order, args.steps)) / args.steps])[0]
+        b = max_over_ranks([sum(timed(two_overlapped, args.steps)) / args.steps])[0]
+        back_to_back = {"two_layers_in_order_ms": a, "two_layers_overlapped_ms": b,
+                        "note": "events around two consecutive layers; overlapped launches the second decode before waiting for the first layer's rows"}
 
     gather_check = gather.check() if gather is not None else None
     launch = layer.launch()
@@ -637,9 +620,8 @@ def our_arm(args, wl):
                        "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
                              % (local_bytes / 1e6),
                        "timing": "CUDA events around decode+merge%s per step, summed over steps (mean; median beside it), max over ranks"
-                                 % (" + output gather; ranks rendezvous (1-element all-reduce) after the flush, before the start "
-                                    "event; a step waits for the previous step's rows after launching its own decode and the last "
-                                    "step also for its own (strict order in ms_per_step_strict)" if world > 1 else "")},
+                                 % (" + output gather (the step ends when all ranks' rows are in this rank's buffer); ranks "
+                                    "rendezvous (1-element all-reduce) after the flush, before the start event" if world > 1 else "")},
             "algorithmic_bytes_per_step": job_bytes,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": peak_src, "kernel": "paged_decode_kernel",
@@ -659,11 +641,10 @@ def our_arm(args, wl):
             "gpu_launches": args.steps * launches_per_step(world, args, launch),
             "gpu_launches_note": "per step: paged_decode_kernel%s%s + stream_read_kernel (L2 flush)"
                                  % ("" if merged_in_kernel else " + merge_segments_kernel",
-                                    " + gather_wait_kernel" if world > 1 and args.gather == "peer" else ""),
+                                    " + gather_signal_kernel" if world > 1 and args.gather == "peer" else ""),
             "clocks": clocks, "wall_s_timed_region": m["wall"],
         }
         if world > 1:
-            line["ms_per_step_strict"] = m["per_strict"]
             line["gather_check"] = gather_check
             line["back_to_back"] = back_to_back
         if one_row_check is not None:
@@ -695,7 +676,7 @@ def gather_mode_of(world, args, launch, gather_check):
     if world == 1:
         return "single GPU"
     if args.gather == "peer":
-        return "decode kernel stores into every peer's buffer (16-byte NVLink peer stores) + flag wait kernel"
+        return "decode kernel stores into every peer's buffer (16-byte NVLink peer stores) + one dependent kernel that raises this rank's flag on the peers and waits for theirs"
     return "ncclAllGather after the decode"
 
 
@@ -783,7 +764,7 @@ def c5_heads(torch, pa, dist, world, rank, stream, measure, max_over_ranks, args
     else:
         single = m["per_step"]
     out = {"workload": desc if not args.c5_batch else desc + " [batch reduced to %d]" % B, "n_gpus": world,
-           "us_per_layer": m["per_step"] * 1e3, "us_per_layer_strict": m["per_strict"] * 1e3,
+           "us_per_layer": m["per_step"] * 1e3,
            "us_decode_kernel_alone": m["per_kernel"] * 1e3,
            "value": full_bytes / (m["per_step"] * 1e-3) / 1e9, "unit": "GB/s (whole layer, all GPUs)",
            "per_gpu_gbs": local_bytes / (m["per_step"] * 1e-3) / 1e9, "scaling": "strong",

@@ -177,7 +177,7 @@ int  pd_device_plan_bind(const pd_device_plan* dp, pd_params* p);
  * PD_KERNEL_TIMEOUT, the CTA that gave up has skipped its arrivals, so the arrival counters of the in-kernel
  * merge inside this device plan may hold partial counts; a later launch of the same plan would merge rows too
  * early or never.  This call clears them (stream-ordered memsets); the next pd_device_plan_upload / _build
- * does so too.  Gathered outputs: see pd_gather_reset. */
+ * does so too. */
 int  pd_device_plan_reset(pd_device_plan* dp, void* stream);
 
 /* Device-side planner.  No counterpart in the reference, whose plan is always cut on the host from host
@@ -265,13 +265,14 @@ int pd_kernel_status(void* stream, unsigned* status);
  * the GPUs of one node, one process per GPU, with the output all-gather done by the decode
  * kernel itself.  Every rank owns gathered-output buffers; the kernel's epilogue (and its
  * in-kernel merge) stores each output row into the step's buffer on EVERY peer with plain 16-byte
- * peer stores over NVLink, and the last CTA raises a per-rank flag on every peer.  pd_gather_wait
- * then enqueues a one-warp kernel that waits (bounded, ~1 s, then PD_KERNEL_TIMEOUT via
- * pd_kernel_status) until all peers' flags of the step have arrived.  No collective library call is
- * involved.  Four buffers are used in rotation (step e fills buffer e mod 4), so a caller may launch
- * step e+1's decode before it waits for step e: the wait then overlaps the next decode, and a step no
- * longer ends with the slowest rank.  Rule for such callers: wait for step e (pd_gather_wait_epoch) and
- * finish reading its buffer before launching step e+2.
+ * peer stores over NVLink.  The kernel neither fences nor signals; a one-warp kernel launched right
+ * behind it as a programmatic dependent raises this rank's flag on every peer once the decode grid has
+ * completed, and pd_gather_wait / pd_gather_wait_epoch enqueue a one-warp kernel that waits (bounded,
+ * ~1 s, then PD_KERNEL_TIMEOUT via pd_kernel_status) until all ranks' flags of the step have arrived.
+ * No collective library call is involved.  Four buffers are used in rotation (step e fills buffer
+ * e mod 4), so a caller may launch step e+1's decode before it waits for step e: the wait then
+ * overlaps the next decode.  Rule for such callers: wait for step e and finish reading its buffer
+ * before launching step e+2.
  *   pd_gather_create   allocates this rank's block (four output buffers in rotation + flags)
  *   pd_gather_export   writes the block's CUDA IPC handle (pd_gather_handle_bytes() bytes)
  *   pd_gather_connect  takes all ranks' handles, rank-major, and maps the peers' blocks
@@ -280,9 +281,15 @@ int pd_kernel_status(void* stream, unsigned* status);
  *       `row_stride_heads` heads (kv-head sharding: offset = rank * local heads; batch sharding:
  *       row_offset = first global row).  p->out is ignored.  Plans with split rows must be
  *       bound by pd_device_plan_bind (in-kernel merge).
+ *   pd_paged_decode_gather_sync  the same, and the kernel behind the decode also waits (bounded) for all
+ *       ranks' flags of this step: when it has run, the whole gathered layer is in the local buffer.  One
+ *       dependent launch instead of two (announcement + pd_gather_wait), for callers that do not overlap
+ *       the wait with anything.
  *   pd_gather_buffer   the local gathered buffer number `which` (0..3: step mod 4; -1 = last step)
- *   pd_gather_reset    after a PD_KERNEL_TIMEOUT: clears the grid's arrival counter, which a CTA that
- *                      gave up has left short (see pd_device_plan_reset) */
+ *   pd_gather_wait     the wait for the last step; pd_gather_wait_epoch for a step the caller names
+ *       (steps are numbered 1, 2, ... by pd_gather_epoch).  Waiting for a step that no peer ever
+ *       signals ends after the bounded ~1 s with PD_KERNEL_TIMEOUT in pd_kernel_status; the context
+ *       stays usable and nothing in the group needs resetting (flags carry step numbers). */
 typedef struct pd_gather_group pd_gather_group;
 int      pd_gather_create(int world, int rank, size_t out_bytes, pd_gather_group** out);
 void     pd_gather_destroy(pd_gather_group* g);
@@ -293,19 +300,10 @@ void*    pd_gather_buffer(const pd_gather_group* g, int which);
 unsigned pd_gather_epoch(const pd_gather_group* g);
 int      pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g,
                                 int row_stride_heads, int head_offset, int row_offset, void* stream);
+int      pd_paged_decode_gather_sync(int dtype, const pd_params* p, int num_pages, pd_gather_group* g,
+                                     int row_stride_heads, int head_offset, int row_offset, void* stream);
 int      pd_gather_wait(pd_gather_group* g, void* stream);
-int      pd_gather_reset(pd_gather_group* g, void* stream);
-/* The same wait for a step the caller names (steps are numbered 1, 2, ... by pd_gather_epoch): lets a
- * pipelined caller wait for step k's rows while step k+1 is already in flight.  Waiting for a step
- * that no peer ever signals ends after the bounded ~1 s with PD_KERNEL_TIMEOUT in pd_kernel_status;
- * the context stays usable. */
 int      pd_gather_wait_epoch(pd_gather_group* g, unsigned epoch, void* stream);
-/* By default the decode kernel only signals and pd_gather_wait enqueues the separate one-warp wait
- * kernel, so other work (the next step's decode) can sit between the decode and the point where the
- * gathered rows are needed.  With `on` = 1 the decode kernel's last CTA itself waits (bounded) for all
- * peers' flags before the kernel ends and pd_gather_wait has nothing left to do; the step then ends
- * with the slowest rank. */
-int      pd_gather_set_wait_in_kernel(pd_gather_group* g, int on);
 
 /* read_kernel of the reference's benchmark (bench/bench_decode.cu:69-78, "copy" mode
  * :224-240): a read-only streaming pass over `bytes` of device memory with `blocks`

@@ -101,10 +101,9 @@ SIGNATURES = {
     "pd_gather_buffer": (_vp, [_vp, C.c_int]),
     "pd_gather_epoch": (C.c_uint, [_vp]),
     "pd_paged_decode_gather": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    "pd_paged_decode_gather_sync": (C.c_int, [C.c_int, C.POINTER(pd_params), C.c_int, _vp, C.c_int, C.c_int, C.c_int, _vp]),
     "pd_gather_wait": (C.c_int, [_vp, _vp]),
-    "pd_gather_reset": (C.c_int, [_vp, _vp]),
     "pd_gather_wait_epoch": (C.c_int, [_vp, C.c_uint, _vp]),
-    "pd_gather_set_wait_in_kernel": (C.c_int, [_vp, C.c_int]),
     "pd_stream_read": (C.c_int, [_vp, C.c_size_t, C.c_int, _vp]),
     "pd_append_tokens": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                    C.c_float, C.c_float, _vp]),

@@ -66,9 +66,10 @@ constexpr unsigned ST_WORKSPACE      = 6;  // the plan has more segments than th
 
 // Where outputs go.  world == 0: to pd_params::out, [batch][num_q_heads][128].  world > 0: this
 // GPU's rows are one slice of a layout gathered over `world` GPUs of the node, and every output
-// is stored straight into the gathered buffer of every peer (plain peer stores over NVLink; the
-// local buffer is out[rank]).  When the last CTA of the grid is done, flags[r][rank] = epoch tells
-// peer r that this rank's slice has landed.  No collective call follows the kernel.
+// is stored straight into the gathered buffer of every peer (plain 16-byte peer stores over NVLink; the
+// local buffer is out[rank]).  The kernel itself neither fences nor signals: gather_signal_kernel, a
+// programmatic dependent launched right behind it, raises this rank's flag on every peer once this grid
+// has completed (all its stores performed), and gather_wait_kernel waits for the peers' flags.
 // Optional per-kv-head dequantisation scales (device arrays of num_kv_heads floats, or null: the
 // per-tensor pd_params::k_scale / v_scale apply).  The reference has one scale per tensor only.
 struct HeadScales {
@@ -95,11 +96,10 @@ struct GatherOut {
     int       row_stride;    // query heads per row of the gathered layout
     int       head_offset;   // first head of this rank's slice within a row (kv-head sharding)
     int       row_offset;    // first row of this rank's slice (batch sharding)
-    unsigned  epoch;
-    int       wait_in_kernel;   // the grid's last CTA also waits (bounded) for every peer's flag before it exits
     __half*   out[MAX_GATHER];
-    unsigned* flags[MAX_GATHER];
-    unsigned* done;          // CTA arrival counter in local memory, zero between launches
+};
+struct GatherFlags {
+    unsigned* flags[MAX_GATHER];   // flags[r]: the flag array in rank r's memory, one word per sender
 };
 
 __device__ __forceinline__ size_t out_index(const pd_params& p, const GatherOut& gp, int row, int head) {
@@ -602,37 +602,6 @@ __device__ __forceinline__ void merge_item(const pd_params& p, const GatherOut& 
     }
 }
 
-// Called by one thread per CTA after the CTA's outputs are stored and fenced.  The CTA that
-// completes the count re-arms the counter and raises this rank's flag on every peer.
-__device__ __forceinline__ void signal_peers(const GatherOut& gp, unsigned* status) {
-    const unsigned seen = atomicAdd(gp.done, 1u);
-    if (seen == gridDim.x - 1) {
-        *gp.done = 0;
-        __threadfence_system();
-        for (int r = 0; r < gp.world; r++) {
-            volatile unsigned* f = gp.flags[r] + gp.rank;
-            *f = gp.epoch;
-        }
-        if (gp.wait_in_kernel) {
-            // The kernel ends only when every peer's slice has landed here too, so the stream that
-            // ran it may read the gathered buffer next.  Bounded like every other wait.
-            const volatile unsigned* mine = gp.flags[gp.rank];
-            const long long t0 = clock64();
-            for (int r = 0; r < gp.world; r++) {
-                while (static_cast<int>(mine[r] - gp.epoch) < 0) {
-                    if (clock64() - t0 > (1ll << 31)) {
-                        atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
-                        return;
-                    }
-                    __nanosleep(64);
-                }
-            }
-            // peers' rows arrived through this GPU's L2; the kernel boundary that follows is what
-            // later readers order against, so no further fence is needed here
-        }
-    }
-}
-
 // ---- decode kernel ---------------------------------------------------------------
 
 template<typename KV, int GROUP, typename C>
@@ -672,10 +641,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int seg_begin = p.cta_seg_begin[blockIdx.x];
     const int seg_end   = p.cta_seg_begin[blockIdx.x + 1];
-    if (seg_begin >= seg_end) {
-        if (gp.world && threadIdx.x == 0) signal_peers(gp, status);   // an idle CTA still counts towards "grid done"
-        return;
-    }
+    if (seg_begin >= seg_end) return;
     if (seg_limit > 0 && seg_end > seg_limit) {
         // A workspace of fixed size (the built-in one) and a plan with more segments than the caller
         // declared: this CTA's partial rows would land outside it.  Nothing is stored; the status word says so.
@@ -1067,13 +1033,6 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         atomicAdd(st.slots + 2 * blockIdx.x + 1, static_cast<unsigned long long>(tiles_done));
         if (blockIdx.x == 0) atomicAdd(st.slots + 2 * gridDim.x, 1ull);
     }
-    if (gp.world && alive) {
-        // Gathered output: this CTA's stores are ordered before its count (device scope); the CTA
-        // that completes the count issues the one system-scope fence ahead of the flags, which by
-        // cumulativity covers every store counted before it.
-        __threadfence();
-        if (consumer_sync() && tid == 0) signal_peers(gp, status);
-    }
 }
 
 // ---- merge kernel -------------------------------------------------------------------
@@ -1183,20 +1142,57 @@ merge_segments_kernel(const __grid_constant__ pd_params p, const int seg_limit)
 // Waits (bounded) until every peer's flag has reached `epoch`: their slices are in this GPU's
 // gathered buffer.  One warp, lane r watches peer r.  Gives up after about a second and records
 // ST_GATHER_TIMEOUT << 24 | peer in the status word; the context stays usable.
+// Raises flags[r][rank] = epoch on every rank r.  Launched as a programmatic dependent right behind the decode
+// kernel whose rows it announces: its warp may be resident early, but it does nothing until that grid has
+// completed and its stores, the ones into the peers' buffers included, have been performed
+// (griddepcontrol.wait); the system-scope fence then orders them before the flags for whoever polls them.
+// wait_flags != null: the same warp then waits (bounded) until every rank's flag in this GPU's own array has
+// reached the epoch, i.e. the whole gathered layer is here - one dependent launch instead of two for callers
+// that want the step complete before anything else runs.
+__global__ void gather_signal_kernel(const __grid_constant__ GatherFlags gf, int world, int rank, unsigned epoch,
+                                     const unsigned* wait_flags, unsigned* status)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();
+    volatile unsigned* f = gf.flags[r] + rank;
+    *f = epoch;
+    if (wait_flags) {
+        const volatile unsigned* w = wait_flags + r;
+        const long long t0 = clock64();
+        while (static_cast<int>(*w - epoch) < 0) {
+            if (clock64() - t0 > (1ll << 31)) {
+                atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
+                break;
+            }
+            __nanosleep(100);
+        }
+        __threadfence_system();
+    }
+}
+
+// Launched as a programmatic dependent of the kernel before it in the stream (the decode whose rows it waits
+// for, or any other): its one warp may be resident and polling while that kernel drains, which takes the
+// launch latency out of the path; it returns only after that kernel has completed as well
+// (griddepcontrol.wait), so whatever follows in the stream sees both the local and the peers' rows.
 __global__ void gather_wait_kernel(const unsigned* flags, int world, unsigned epoch, unsigned* status)
 {
     const int r = threadIdx.x;
-    if (r >= world) return;
-    const volatile unsigned* f = flags + r;
-    const long long t0 = clock64();
-    while (static_cast<int>(*f - epoch) < 0) {
-        if (clock64() - t0 > (1ll << 31)) {
-            atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
-            break;
+    if (r < world) {
+        const volatile unsigned* f = flags + r;
+        const long long t0 = clock64();
+        while (static_cast<int>(*f - epoch) < 0) {
+            if (clock64() - t0 > (1ll << 31)) {
+                atomicCAS(status, 0u, (ST_GATHER_TIMEOUT << 24) | static_cast<unsigned>(r));
+                break;
+            }
+            __nanosleep(200);
         }
-        __nanosleep(100);
+        __threadfence_system();
     }
-    __threadfence_system();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace pdk

@@ -1316,11 +1316,9 @@ struct pd_gather_group {
     int world = 0, rank = 0;
     size_t out_bytes = 0, block_bytes = 0;
     unsigned epoch = 0;
-    bool wait_in_kernel = false;
     char* block[pdk::MAX_GATHER] = {};      // block[rank] is the local allocation, the rest are IPC mappings
     bool connected = false;
     size_t flags_offset() const { return GATHER_BUFFERS * out_bytes; }
-    size_t done_offset() const { return GATHER_BUFFERS * out_bytes + 128; }
 };
 
 extern "C" {
@@ -1388,8 +1386,10 @@ void* pd_gather_buffer(const pd_gather_group* g, int which) {
 
 unsigned pd_gather_epoch(const pd_gather_group* g) { return g ? g->epoch : 0; }
 
-int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g, int row_stride_heads,
-                           int head_offset, int row_offset, void* stream) {
+}  // extern "C"
+namespace {
+int decode_gather_impl(int dtype, const pd_params* p, int num_pages, pd_gather_group* g, int row_stride_heads,
+                       int head_offset, int row_offset, bool wait, void* stream) {
     if (!g || !p) return set_error(PD_INVALID_ARGUMENT, "decode_gather: null argument");
     if (!g->connected) return set_error(PD_INVALID_ARGUMENT, "decode_gather: call pd_gather_connect first");
     if (row_stride_heads < p->num_q_heads + head_offset || head_offset < 0 || row_offset < 0)
@@ -1399,52 +1399,69 @@ int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gath
     if (p->num_ctas <= 0 || p->batch <= 0) return set_error(PD_INVALID_ARGUMENT, "decode_gather: empty plan");
     g->epoch++;
     pdk::GatherOut go{};
+    pdk::GatherFlags gf{};
     go.world = g->world; go.rank = g->rank;
     go.row_stride = row_stride_heads; go.head_offset = head_offset; go.row_offset = row_offset;
-    go.epoch = g->epoch;
-    go.wait_in_kernel = g->wait_in_kernel ? 1 : 0;
     for (int r = 0; r < g->world; r++) {
         go.out[r]   = reinterpret_cast<__half*>(g->block[r] + (g->epoch % GATHER_BUFFERS) * g->out_bytes);
-        go.flags[r] = reinterpret_cast<unsigned*>(g->block[r] + g->flags_offset());
+        gf.flags[r] = reinterpret_cast<unsigned*>(g->block[r] + g->flags_offset());
     }
-    go.done = reinterpret_cast<unsigned*>(g->block[g->rank] + g->done_offset());
     // Gathered rows are written by the decode kernel itself, so split rows are merged in-kernel here
     // even where the plan preferred the separate merge kernel; workspaces bound by
     // pd_device_plan_bind always carry the arrival counters that needs.
     pd_params local = *p;
     if (local.needs_merge) local.needs_merge = pdk::MERGE_IN_KERNEL;
     const int rc = decode_impl(dtype, &local, num_pages, go, stream);
-    if (rc != PD_OK) g->epoch--;
-    return rc;
-}
-
-// After a PD_KERNEL_TIMEOUT: a CTA that gave up never counted itself, so the grid counter may be left
-// between zero and the grid size; the next launch would then signal the peers too early or never.
-int pd_gather_reset(pd_gather_group* g, void* stream) {
-    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_reset: null argument");
-    PD_CUDA(cudaMemsetAsync(g->block[g->rank] + g->done_offset(), 0, sizeof(unsigned), static_cast<cudaStream_t>(stream)));
+    if (rc != PD_OK) { g->epoch--; return rc; }
+    // the announcement: one warp, launched as a programmatic dependent of the decode kernel
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const unsigned* wait_flags = wait ? reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()) : nullptr;
+    unsigned* status = nullptr;
+    if (int rc2 = status_word(&status)) return rc2;
+    PD_CUDA(cudaLaunchKernelEx(&cfg, pdk::gather_signal_kernel, gf, g->world, g->rank, g->epoch, wait_flags, status));
     return PD_OK;
 }
+}  // namespace
+extern "C" {
 
-int pd_gather_set_wait_in_kernel(pd_gather_group* g, int on) {
-    if (!g) return set_error(PD_INVALID_ARGUMENT, "gather: null argument");
-    g->wait_in_kernel = on != 0;
-    return PD_OK;
+int pd_paged_decode_gather(int dtype, const pd_params* p, int num_pages, pd_gather_group* g, int row_stride_heads,
+                           int head_offset, int row_offset, void* stream) {
+    return decode_gather_impl(dtype, p, num_pages, g, row_stride_heads, head_offset, row_offset, false, stream);
+}
+
+int pd_paged_decode_gather_sync(int dtype, const pd_params* p, int num_pages, pd_gather_group* g, int row_stride_heads,
+                                int head_offset, int row_offset, void* stream) {
+    return decode_gather_impl(dtype, p, num_pages, g, row_stride_heads, head_offset, row_offset, true, stream);
 }
 
 int pd_gather_wait_epoch(pd_gather_group* g, unsigned epoch, void* stream) {
     if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_wait: null argument");
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
-    pdk::gather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()), g->world, epoch, status);
-    PD_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    PD_CUDA(cudaLaunchKernelEx(&cfg, pdk::gather_wait_kernel,
+                               reinterpret_cast<const unsigned*>(g->block[g->rank] + g->flags_offset()), g->world, epoch, status));
     return PD_OK;
 }
 
 int pd_gather_wait(pd_gather_group* g, void* stream) {
     if (!g) return set_error(PD_INVALID_ARGUMENT, "gather_wait: null argument");
-    if (g->wait_in_kernel) return PD_OK;   // the decode kernel already waited before it ended
     return pd_gather_wait_epoch(g, g->epoch, stream);
 }
 

@@ -96,8 +96,9 @@ def gather_outputs(out_local, mode, group=None, rows=None):
 
 class GatherGroup:
     """Gathered outputs without a collective call: every rank's decode kernel stores its rows into
-    every peer's buffer (peer stores over NVLink) and raises a flag; `wait` enqueues the bounded
-    flag wait.  One process per GPU; the IPC handles travel through the torch process group."""
+    every peer's buffer (peer stores over NVLink), a one-warp kernel behind it raises this rank's flag on
+    every peer, and `wait` / `wait_epoch` enqueue the bounded wait for all ranks' flags.  One process per
+    GPU; the IPC handles travel through the torch process group."""
 
     def __init__(self, out_bytes, group=None):
         import ctypes as C
@@ -149,15 +150,13 @@ class GatherGroup:
     def __del__(self):
         self.close()
 
-    def decode(self, dtype, params, row_stride_heads, head_offset=0, row_offset=0, stream=0, num_pages=0):
-        self._lib.check(self._lib.lib().pd_paged_decode_gather(int(dtype), self._C.byref(params), num_pages, self._h,
-                                                               row_stride_heads, head_offset, row_offset, stream))
-
-    def set_wait_in_kernel(self, on):
-        """off (default): the decode kernel only signals and `wait` / `wait_epoch` enqueue a separate wait
-        kernel, so the next step's decode can run ahead of the wait; on: the decode kernel itself ends only
-        when all peers' rows have landed."""
-        self._lib.check(self._lib.lib().pd_gather_set_wait_in_kernel(self._h, int(bool(on))))
+    def decode(self, dtype, params, row_stride_heads, head_offset=0, row_offset=0, stream=0, num_pages=0, sync=False):
+        """One layer with its rows stored into every rank's buffer.  sync=False: returns after the announcement
+        is queued; `wait` / `wait_epoch` wait for the peers whenever the caller wants.  sync=True: the kernel
+        behind the decode also waits for all ranks' rows (one launch fewer)."""
+        fn = self._lib.lib().pd_paged_decode_gather_sync if sync else self._lib.lib().pd_paged_decode_gather
+        self._lib.check(fn(int(dtype), self._C.byref(params), num_pages, self._h, row_stride_heads, head_offset,
+                           row_offset, stream))
 
     def wait(self, stream=0):
         self._lib.check(self._lib.lib().pd_gather_wait(self._h, stream))
@@ -169,10 +168,6 @@ class GatherGroup:
     @property
     def epoch(self):
         return self._lib.lib().pd_gather_epoch(self._h)
-
-    def reset(self, stream=0):
-        """After a KernelTimeout: clear the grid's arrival counter."""
-        self._lib.check(self._lib.lib().pd_gather_reset(self._h, stream))
 
     def buffer_ptr(self, which=-1):
         """Device pointer of the local gathered buffer (which = step mod 4, -1 = the one the last decode filled)."""

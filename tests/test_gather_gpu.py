@@ -91,17 +91,18 @@ def _run_rank(rank, world, torch, pa, sharding, mode):
     full_bytes = B * hq * d * 2
     gg = sharding.GatherGroup(full_bytes)
     got = None
-    for step in range(4):
-        gg.set_wait_in_kernel(step < 2)            # then the signal-only kernel + separate wait kernel
-        gg.decode(pa.KVDtype.FP16, p, hq, head_off, row_off, 0, cfg.num_pages)
-        gg.wait(0)
+    for step in range(6):                          # more steps than buffers in the rotation
+        # alternately: announce only + separate wait kernel, and announce-and-wait in one kernel
+        gg.decode(pa.KVDtype.FP16, p, hq, head_off, row_off, 0, cfg.num_pages, sync=bool(step & 1))
+        if not step & 1:
+            gg.wait(0)
         torch.cuda.synchronize()
         assert pa.kernel_status() == 0
         buf = _view(torch, gg.buffer_ptr(-1), full_bytes).view(torch.float16).view(B, hq, d)
         got = buf.float().cpu().numpy()
         if step == 0:
             first = got.copy()
-        assert np.array_equal(got, first)          # both buffers, every step: the same bits
+        assert np.array_equal(got, first)          # every buffer, every step: the same bits
     return got, gg, cache
 
 
