@@ -214,6 +214,14 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
                  " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
                  :: "r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "l"(pol) : "memory");
 }
+// Four rows of a 2-D tensor map (box: `cols` x 1 row), gathered into four consecutive 128-byte rows of shared
+// memory: one copy instruction for four tokens whose rows lie anywhere in the pool (pages of 1 or 2 tokens).
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, uint32_t bar, int col,
+                                            int r0, int r1, int r2, int r3, uint64_t pol) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint"
+                 " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(pol) : "memory");
+}
 // Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -608,6 +616,7 @@ template<typename KV, int GROUP, typename C>
 __global__ void __launch_bounds__((C::WARPS + 1) * 32, C::MIN_CTAS)
 paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__ CUtensorMap k_map,
                     const __grid_constant__ CUtensorMap v_map, const int btl /* log2(tokens per box) */,
+                    const int row_gather /* boxes are four rows gathered one by one: the maps are 2-D [pool row][dims] */,
                     const int seg_limit /* segments the split-row workspace holds; 0 = sized by the plan's owner */,
                     unsigned* __restrict__ status, const __grid_constant__ GatherOut gp,
                     const __grid_constant__ HeadScales hs, const __grid_constant__ CtaStats st)
@@ -690,7 +699,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         };
         // Issue the copies of one tile: lanes [lane0, lane0 + nb) own one box each when
         // the tile has <= 32 boxes, otherwise every lane walks boxes lane, lane+32, ...
-        auto issue_tile = [&](const int4& sg, int tile_tok, int my_page, int lane0, const int* bt) -> bool {
+        auto issue_tile = [&](const int4& sg, int tile_tok, int4 my_page, int lane0, const int* bt) -> bool {
             const int stage = p_stage;
             if (!mbar_wait(empty_bar(stage), p_phase ^ 1)) { if (lane == 0) fail(ST_EMPTY_TIMEOUT); return false; }
             if (*abort_flag) return false;
@@ -708,7 +717,25 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
             const uint32_t k_dst = pipe + stage * S::STAGE_BYTES;
             const uint32_t v_dst = k_dst + S::TILE_BYTES;
             const int head_coord = S::HEADS == 1 ? sg.y : 0;   // a head-fused box spans kv heads 0..7
-            auto copy_box = [&](int j, int page) {
+            auto copy_box = [&](int j, int4 page4) {
+                const int page = page4.x;
+                if (S::HEADS == 1 && row_gather) {
+                    // pages smaller than four tokens: the box's four tokens are four rows of the pool, looked up
+                    // one by one (tokens past the segment's end repeat its last token; their rows are masked)
+                    const int t0 = tile_tok + 4 * j, last = sg.w - 1;
+                    const int pg[4] = {page4.x, page4.y, page4.z, page4.w};
+                    int r[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        r[i] = (pg[i] * p.num_kv_heads + head_coord) * ps + min(t0 + i, last) % ps;
+                    constexpr int PANELS = sizeof(KV);
+#pragma unroll
+                    for (int h = 0; h < PANELS; h++) {
+                        tma_gather4(k_dst + j * box_bytes + h * 512, &k_map, full_bar(stage), 64 * h, r[0], r[1], r[2], r[3], pol);
+                        tma_gather4(v_dst + j * box_bytes + h * 512, &v_map, full_bar(stage), 64 * h, r[0], r[1], r[2], r[3], pol);
+                    }
+                    return;
+                }
                 const int tok_in_page = (tile_tok + (j << btl)) % ps;
                 if constexpr (FP8) {
                     tma_load_4d(k_dst + j * box_bytes, &k_map, full_bar(stage), 0, tok_in_page, head_coord, page, pol);
@@ -723,7 +750,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 if (j >= 0 && j < nb) copy_box(j, my_page);
             } else {
                 for (int j = lane; j < nb; j += 32)
-                    copy_box(j, __ldg(bt + (tile_tok + (j << btl)) / ps));
+                    copy_box(j, make_int4(__ldg(bt + (tile_tok + (j << btl)) / ps), 0, 0, 0));
             }
             issued++;
             if (++p_stage == nst) { p_stage = 0; p_phase ^= 1; }
@@ -737,11 +764,22 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
         int4 sg  = __ldg(segments + seg);
         const int* bt = table_of(sg.x);
         int  tok = sg.z;
+        // the page id of this lane's box (row_gather: of each of its four tokens)
         auto page_of = [&](const int4& s, const int* table, int chunk_tok) {
             const int t = chunk_tok + (lane << btl);
-            return (bpt <= 32 && t < s.w) ? __ldg(table + t / ps) : 0;
+            int4 pg = make_int4(0, 0, 0, 0);
+            if (bpt <= 32 && t < s.w) {
+                pg.x = __ldg(table + t / ps);
+                if (S::HEADS == 1 && row_gather) {
+                    const int last = s.w - 1;
+                    pg.y = __ldg(table + min(t + 1, last) / ps);
+                    pg.z = __ldg(table + min(t + 2, last) / ps);
+                    pg.w = __ldg(table + min(t + 3, last) / ps);
+                }
+            }
+            return pg;
         };
-        int page = page_of(sg, bt, tok);
+        int4 page = page_of(sg, bt, tok);
         while (ok && seg < seg_end) {
             // Look one chunk ahead (possibly into the next segment) so its page ids are
             // in flight while this chunk's copies are issued.
@@ -752,7 +790,7 @@ paged_decode_kernel(const __grid_constant__ pd_params p, const __grid_constant__
                 n_seg = seg + 1;
                 if (n_seg < seg_end) { n_sg = __ldg(segments + n_seg); n_bt = table_of(n_sg.x); n_tok = n_sg.z; }
             }
-            const int n_page = n_seg < seg_end ? page_of(n_sg, n_bt, n_tok) : 0;
+            const int4 n_page = n_seg < seg_end ? page_of(n_sg, n_bt, n_tok) : make_int4(0, 0, 0, 0);
             for (int ti = 0; ti < chunk_tiles; ti++) {
                 const int tile_tok = tok + ti * S::TILE;
                 if (tile_tok >= sg.w) break;

@@ -72,17 +72,17 @@ template<> struct DefaultConfig<__nv_fp8_e4m3> { using type = ShapeOf<PD_B200_FP
 struct KernelInfo {
     const void* fn;
     int tile, threads, smem, per_sm, stages;
-    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, int, unsigned*, const pdk::GatherOut&,
+    void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, int, int, unsigned*, const pdk::GatherOut&,
                    const pdk::HeadScales&, const pdk::CtaStats&, cudaStream_t);
     void (*merge)(const pd_params&, int, cudaStream_t);
 };
 
 template<typename KV, int GROUP, typename C>
-void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl, int seg_limit,
+void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl, int row_gather, int seg_limit,
                    unsigned* status, const pdk::GatherOut& gather, const pdk::HeadScales& scales, const pdk::CtaStats& stats,
                    cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
-    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, seg_limit, status, gather, scales, stats);
+    pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, row_gather, seg_limit, status, gather, scales, stats);
 }
 // The merge kernel is launched as a programmatic dependent of the decode kernel before it: its CTAs are
 // placed while the decode grid drains and wait inside the kernel (griddepcontrol.wait) until that grid is
@@ -248,8 +248,10 @@ unsigned gcd_u(unsigned a, unsigned b) { while (b) { const unsigned t = a % b; a
 //   fp16: 5-D  (64 dims, token, panel, kv head, page), box (64, 2^btl, 2, 1, 1)
 //   fp8 : 4-D  (128 dims, token, kv head, page),       box (128, 2^btl, 1, 1)
 // so a box lands in shared memory as [panel][token][128 bytes] under the 128-byte swizzle.
+//   row_gather (pages of fewer than 4 tokens): 2-D (row bytes, pool rows = page x kv head x token), box
+//   (128 bytes, 1 row) for cp.async.bulk.tensor ... tile::gather4, which fetches four such rows per copy.
 int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages, int num_kv_heads,
-                    int page_size, int btl, int box_heads = 1) {
+                    int page_size, int btl, int box_heads = 1, bool row_gather = false) {
     EncodeTiledFn enc;
     if (int rc = encode_fn(&enc)) return rc;
     if (reinterpret_cast<uintptr_t>(pool) % 16 != 0)
@@ -258,7 +260,16 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* pool, int num_pages
     const cuuint64_t row = dtype == PD_FP16 ? 256 : 128;
     const CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     CUresult r;
-    if (dtype == PD_FP16) {
+    if (row_gather) {
+        const cuuint64_t rows = std::min<cuuint64_t>(pages * num_kv_heads * page_size, 1ull << 31);
+        const cuuint64_t dims[2]    = {128, rows};
+        const cuuint64_t strides[1] = {row};
+        const cuuint32_t box[2]     = {dtype == PD_FP16 ? 64u : 128u, 1};
+        const cuuint32_t estr[2]    = {1, 1};
+        r = enc(map, dtype == PD_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                const_cast<void*>(pool), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (dtype == PD_FP16) {
         const cuuint64_t dims[5]    = {64, static_cast<cuuint64_t>(page_size), 2, static_cast<cuuint64_t>(num_kv_heads), pages};
         const cuuint64_t strides[4] = {row, 128, row * page_size, row * page_size * num_kv_heads};
         const cuuint32_t box[5]     = {64, 1u << btl, 2, static_cast<cuuint32_t>(box_heads), 1};
@@ -1075,16 +1086,20 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     unsigned* status = nullptr;
     if (int rc = status_word(&status)) return rc;
 
-    // A box is the largest run of tokens that never straddles a page or a tile.
+    // A box is the largest run of tokens that never straddles a page or a tile.  Where that is fewer than four
+    // tokens (pages of 1, 2, 3, 5, ... tokens) the (row, kv head) kernel gathers four rows per copy instead:
+    // one TMA operation per token would leave the copy engine, not DRAM, as the limit.
     const unsigned box_tokens = gcd_u(static_cast<unsigned>(p->page_size), static_cast<unsigned>(k->tile));
     int btl = 0;
     while ((1u << (btl + 1)) <= box_tokens) btl++;
+    const bool row_gather = box_heads == 1 && btl < 2;
+    if (row_gather) btl = 2;
     CUtensorMap k_map, v_map;
-    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads)) return rc;
-    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads)) return rc;
+    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads, row_gather)) return rc;
+    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads, row_gather)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    k->launch(*p, k_map, v_map, btl, 0, status, gather, scales, pdk::CtaStats{stats_slots}, stream);
+    k->launch(*p, k_map, v_map, btl, row_gather ? 1 : 0, 0, status, gather, scales, pdk::CtaStats{stats_slots}, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, 0, stream);
@@ -1215,15 +1230,17 @@ int pd_paged_decode_static(int dtype, const pd_params* p, int num_segments, int 
     const unsigned box_tokens = gcd_u(static_cast<unsigned>(p->page_size), static_cast<unsigned>(k->tile));
     int btl = 0;
     while ((1u << (btl + 1)) <= box_tokens) btl++;
+    const bool row_gather = btl < 2;
+    if (row_gather) btl = 2;
     CUtensorMap k_map, v_map;
-    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
-    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl)) return rc;
+    if (int rc = make_tensor_map(&k_map, dtype, p->k_cache, num_pages, p->num_kv_heads, p->page_size, btl, 1, row_gather)) return rc;
+    if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, 1, row_gather)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     // The kernels compare the declared count with the plan they walk (cta_seg_begin on the device): a CTA
     // whose segments lie beyond it stores nothing and reports ST_WORKSPACE instead of writing past the array.
     const int seg_limit = std::max(num_segments, 1);
-    k->launch(local, k_map, v_map, btl, seg_limit, d_status ? d_status : scratch->status, pdk::GatherOut{},
+    k->launch(local, k_map, v_map, btl, row_gather ? 1 : 0, seg_limit, d_status ? d_status : scratch->status, pdk::GatherOut{},
               pdk::HeadScales{nullptr, nullptr}, pdk::CtaStats{nullptr}, stream);
     PD_CUDA(cudaGetLastError());
     if (local.needs_merge) {
