@@ -46,6 +46,7 @@ WORKLOADS = {
     "small": (0, 8, 8192, 32, 8, 16, "profiling case: batch 8 x 8192 fp16 (268 MB of KV, larger than L2)"),
     "small-fp8": (1, 16, 8192, 32, 8, 16, "profiling case: batch 16 x 8192 fp8 (268 MB of KV)"),
     "small-wide": (0, 64, 1024, 32, 8, 16, "profiling case of the head-fused schedule: batch 64 x 1024 fp16 (268 MB of KV)"),
+    "small-wide-fp8": (1, 64, 2048, 32, 8, 16, "profiling case of the head-fused e4m3 schedule: batch 64 x 2048 fp8 (268 MB of KV)"),
     "single": (0, 1, 16384, 32, 8, 16, "profiling case of the merge kernel: one sequence of 16384 tokens spread over the grid"),
 }
 DTYPE_NAMES = {0: "f16", 1: "f8e4m3"}
@@ -432,7 +433,7 @@ def our_arm(args, wl):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pa.set_adaptive_cut(args.adaptive_cut == "on")
-    if args.workload == "small-wide":
+    if args.workload in ("small-wide", "small-wide-fp8"):
         pa.set_head_fused(2)      # the profiling case of the head-fused kernel is too short for it to be chosen by itself
     stream = torch.cuda.current_stream().cuda_stream
 

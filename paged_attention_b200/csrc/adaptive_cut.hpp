@@ -132,7 +132,13 @@ void fold_readings(RateTable* t, cudaStream_t stream) {
         if (rate[c] > 0.0) { lo = std::min(lo, rate[c]); hi = std::max(hi, rate[c]); }
     if (hi > 1.5 * lo) return;
     if (t->weights.empty()) t->weights.assign(n, 1.0f);
-    const double gain = t->updates < 4 ? 0.5 : 0.3;
+#ifndef PD_B200_CUT_GAIN_EARLY
+#define PD_B200_CUT_GAIN_EARLY 0.5
+#endif
+#ifndef PD_B200_CUT_GAIN
+#define PD_B200_CUT_GAIN 0.3
+#endif
+    const double gain = t->updates < 4 ? PD_B200_CUT_GAIN_EARLY : PD_B200_CUT_GAIN;
     double wsum = 0.0;
     for (int c = 0; c < n; c++) {
         if (!(rate[c] > 0.0)) { wsum += t->weights[c]; continue; }

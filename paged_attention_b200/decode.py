@@ -113,7 +113,10 @@ class DecodePlan:
 
     def __del__(self):
         if getattr(self, "_owned", False) and self._h:
-            _lib.lib().pd_plan_free(self._h)
+            try:
+                _lib.lib().pd_plan_free(self._h)
+            except Exception:      # interpreter shutdown: the module is already gone
+                pass
             self._h = None
 
     @property
@@ -198,7 +201,10 @@ class DevicePlan:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            _lib.lib().pd_device_plan_destroy(self._h)
+            try:
+                _lib.lib().pd_device_plan_destroy(self._h)
+            except Exception:      # interpreter shutdown: the module is already gone
+                pass
             self._h = None
 
     def upload(self, plan, group, head_dim, stream=0):
@@ -321,7 +327,10 @@ class PagedKVCache:
             self._h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:          # interpreter shutdown: the module is already gone
+            pass
 
     @staticmethod
     def bytes_per_page(cfg):

@@ -148,7 +148,10 @@ class GatherGroup:
             self._h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:          # interpreter shutdown: the module is already gone
+            pass
 
     def decode(self, dtype, params, row_stride_heads, head_offset=0, row_offset=0, stream=0, num_pages=0, sync=False):
         """One layer with its rows stored into every rank's buffer.  sync=False: returns after the announcement

@@ -79,6 +79,56 @@ def test_append_batch_equals_per_slot_appends(dtype, torch_cuda, pa):
     Bc.close()
 
 
+def test_release_waits_for_a_batched_append_on_another_stream(torch_cuda, pa):
+    """append_batch is stream-ordered and does not wait; release() hands the slot's pages back and zeroes its
+    device-side length with a memset that is not ordered with that stream.  On a non-blocking stream (every
+    torch stream is one) the scatter may still be pending: release must wait for it, so that the freed pages
+    are not rewritten later and the slot's device length ends at zero (a device-side plan reads it)."""
+    torch = torch_cuda
+    from common import device_view
+    hkv, d, ps = 8, 128, 16
+    cfg = pa.PagedKVCache.Config(num_pages=600, page_size=ps, num_kv_heads=hkv, head_dim=d, max_slots=3,
+                                 max_pages_per_slot=300)
+    cache = pa.PagedKVCache(cfg)
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    n = 4096
+    k0 = torch.randn(n, hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+    k1 = torch.randn(n, hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+    k2 = torch.randn(64, hkv, d, device="cuda", dtype=torch.float16, generator=gen)
+    assert cache.admit() == 0 and cache.admit() == 1
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    busy = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    with torch.cuda.stream(side):
+        for _ in range(8):
+            busy.fill_(1)                       # keeps the side stream occupied while the host runs ahead
+        assert cache.append_batch([0, 1], [k0, k1], [k0, k1], [n, n], side.cuda_stream)
+    cache.release(0)                            # host-side at once; must not overtake the scatter on `side`
+    assert cache.admit() == 0
+    assert cache.append(0, k2, k2, 64)          # reuses the pages slot 0 had (default stream)
+    torch.cuda.synchronize()
+    lens = device_view(cache.params().seq_lens, 12, torch).view(torch.int32).tolist()
+    assert lens == [64, n, 0]
+    # slot 0's new tokens are what its pages hold now, not the released sequence's scatter arriving late
+    q = torch.randn(2, 32, d, device="cuda", dtype=torch.float16, generator=gen)
+    out = torch.zeros_like(q)
+    cache.plan_device(2, 32)
+    cache.run(q, out)
+    torch.cuda.synchronize()
+    assert pa.kernel_status() == 0
+    K = [k2.cpu().numpy(), k1.cpu().numpy()]
+    kc = np.zeros(cfg.num_pages * hkv * ps * d, np.uint16)
+    vc = np.zeros_like(kc)
+    bt = np.zeros((2, cfg.max_pages_per_slot), np.int32)
+    for b in range(2):
+        t = cache.block_table(b)
+        bt[b, :len(t)] = t
+        ol.append(0, K[b].view(np.uint16), K[b].view(np.uint16), kc, vc, t, 0, hkv, d, ps)
+    want = ol.paged_decode(1, 0, q.cpu().numpy().view(np.uint16), kc, vc, bt, [64, n], 32, hkv, d, ps)
+    assert float(np.abs(out.float().cpu().numpy() - want).max()) <= TOL
+    cache.close()
+
+
 @pytest.mark.parametrize("fp8", [False, True])
 def test_decoder_binding_on_raw_tensors(fp8, torch_cuda, pa):
     """Inputs built the way the reference's FlashInfer harness builds them
