@@ -100,17 +100,16 @@ int pd_tile_tokens(int dtype, int head_dim, int group, int* out);
 int pd_wave_ctas(int dtype, int head_dim, int group, int* out);
 int pd_default_ctas(int dtype, int head_dim, int group, int* out);
 
-/* Tuning knob without a counterpart in the reference.  fp16 layers with exactly 8 kv heads
- * whose plan came from pd_make_plan (directly or through the cache) normally run the "head-fused"
- * schedule: the device plan also carries the step cut by rows, a tile is 16 tokens of all 8 kv heads
- * (one 32 KB box per page and pool for fp16 instead of eight 4 KB boxes fetched by different CTAs at
- * different times), one consumer warp per kv head, no cross-warp merge.  The plan object and
- * pd_params keep the reference's (row, kv head) format either way.  Modes: 0 never (environment
- * PD_B200_NO_HEAD_FUSED=1 also selects it); 1, the default, where it wins: steps whose rows are cut in
- * at most 4 pieces each over the one-CTA-per-SM grid (batches of about 64 rows and more; with fewer rows
- * every row is spread over dozens of CTAs and the (row, kv head) schedule, which has 8 times as many
- * work items, is faster); 2 whenever the layer allows it (used by tests).  Takes effect at the next
- * decode call. */
+/* Tuning knob without a counterpart in the reference.  Layers with exactly 8 kv heads whose plan came from
+ * pd_make_plan (directly or through the cache) normally run the "head-fused" schedule: the device plan also
+ * carries the step cut by rows, a tile is 16 tokens (fp16 cache) or 32 tokens (e4m3 cache) of all 8 kv heads
+ * (one 32 KB / 16 KB box per page and pool instead of eight boxes fetched by different CTAs at different
+ * times), one consumer warp per kv head, no cross-warp merge.  The plan object and pd_params keep the
+ * reference's (row, kv head) format either way.  Modes: 0 never (environment PD_B200_NO_HEAD_FUSED=1 also
+ * selects it); 1, the default, where it wins: steps whose rows are cut in at most 4 pieces each over the
+ * one-CTA-per-SM grid (batches of about 64 rows and more; with fewer rows every row is spread over dozens of
+ * CTAs and the (row, kv head) schedule, which has 8 times as many work items, is faster); 2 whenever the
+ * layer allows it (used by tests).  Takes effect at the next decode call. */
 int pd_set_head_fused(int mode);
 int pd_head_fused(void);
 /* Second knob without a counterpart in the reference: the adaptive cut.  SMs of one GPU do not stream at
