@@ -128,12 +128,11 @@ const KernelInfo* info_by_group(int group) {
     return nullptr;
 }
 
-// Head-fused tiles (all 8 kv heads of 16 tokens per tile, one consumer warp per kv head); used for
-// fp16 plans made by pd_make_plan when the layer has exactly 8 kv heads: 3 stages of 64 KB, one CTA per
-// SM.  Measured on the batch 64 x 8192 layer: 314 us against 320 us for the (row, kv head) schedule, and
-// 0.9 % instead of 2.6 % over one contiguous page per sequence.  The fp8 cache gains nothing from it
-// (170 us either way at one or two CTAs per SM: the fp8 path is bound by its widening arithmetic, not by
-// DRAM locality), so fp8 keeps the (row, kv head) schedule at three CTAs per SM.
+// Head-fused tiles (all 8 kv heads of one token unit per tile, one consumer warp per kv head); used for
+// plans made by pd_make_plan when the layer has exactly 8 kv heads, for both cache types: 3 stages of
+// 64 KB, one CTA per SM.  Measured on the batch 64 x 8192 fp16 layer: 314 us against 320 us for the
+// (row, kv head) schedule, and 0.9 % instead of 2.6 % over one contiguous page per sequence; on the
+// same layer with the e4m3 cache 164.8 us against 168.7 us.
 template<typename KV> struct FusedConfig;
 template<> struct FusedConfig<__half> { using type = pdk::Config<8, 1, 3, 1, 8>; };
 // e4m3: a warp's unit is 32 tokens, so a tile is 32 tokens of all 8 kv heads: two 16 KB boxes per pool and tile
