@@ -433,7 +433,6 @@ def our_arm(args, wl):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pa.set_adaptive_cut(args.adaptive_cut == "on")
-    pa.set_tail_steal(1 if args.tail_steal == "on" else 0)
     if args.workload in ("small-wide", "small-wide-fp8"):
         pa.set_head_fused(2)      # the profiling case of the head-fused kernel is too short for it to be chosen by itself
     stream = torch.cuda.current_stream().cuda_stream
@@ -617,9 +616,8 @@ def our_arm(args, wl):
                        "pages": "contiguous" if args.contiguous_pages else "scattered (shuffle seed 42)",
                        "plan_of_the_caller": {"ctas": layer.plan.num_ctas, "segments": layer.plan.num_segments, "tile": layer.plan.tile},
                        "launch": launch,
-                       "plan": "uploaded before every untimed step, timed steps reuse the last one; adaptive cut %s; "
-                               "work moving between running CTAs %s"
-                               % ("on" if pa.adaptive_cut() else "off", "on" if pa.tail_steal() else "off"),
+                       "plan": "uploaded before every untimed step, timed steps reuse the last one; adaptive cut %s"
+                               % ("on" if pa.adaptive_cut() else "off"),
                        "l2": "KV per step (%.0f MB) exceeds L2 and a read-only flush of 512 MB runs before every step, outside the events"
                              % (local_bytes / 1e6),
                        "timing": "CUDA events around decode+merge%s per step, summed over steps (mean; median beside it), max over ranks"
@@ -814,8 +812,6 @@ def main():
     ap.add_argument("--no-reference-gpu", action="store_true")
     ap.add_argument("--adaptive-cut", default="on", choices=["on", "off"],
                     help="off: equal shares as in the reference (and no settling steps); profiling runs use it to keep the launch count small")
-    ap.add_argument("--tail-steal", default="on", choices=["on", "off"],
-                    help="off: CTAs of a head-fused launch keep the shares the plan gave them")
     ap.add_argument("--no-c5", action="store_true", help="skip the kv-head-sharded 70B-shaped layer after the headline")
     ap.add_argument("--c5-batch", type=int, default=0, help="batch of that layer (default: the workload's 256)")
     args = ap.parse_args()

@@ -112,21 +112,6 @@ int pd_default_ctas(int dtype, int head_dim, int group, int* out);
  * layer allows it (used by tests).  Takes effect at the next decode call. */
 int pd_set_head_fused(int mode);
 int pd_head_fused(void);
-/* Third knob without a counterpart in the reference, for the head-fused schedule: work moves between CTAs
- * while the kernel runs.  The planner's cut is fixed before the launch, but CTAs of one launch finish several
- * percent apart (SMs stream at different rates, and the rates move from launch to launch), and while the last
- * ones finish DRAM is idle in part.  With this on, a CTA that has issued all its own tiles takes the back half
- * of the unissued tiles of the CTA that has most left (one compare-and-swap on a word per CTA; nothing waits on
- * another CTA), streams it as one more piece of that row and the row's last piece to finish merges them all.
- * Used for steps whose rows the decode kernel merges itself (needs_merge 0 or 2 of the head-fused cut).  Which
- * pieces move differs from launch to launch, so outputs of two runs agree within rounding (2.5e-4), not bit for
- * bit.  Modes: 0 off (environment PD_B200_NO_TAIL_STEAL=1 also selects it), 1 on (default), 2 on with the row
- * cut skewed on purpose (shares alternate 0.6 / 1.4) so that every launch moves work: for tests.  Takes effect
- * at the next pd_device_plan_upload.  pd_tail_steal_count: pieces moved on the current device since the
- * process started (waits for the stream first). */
-int pd_set_tail_steal(int mode);
-int pd_tail_steal(void);
-int pd_tail_steal_count(void* stream, unsigned long long* count);
 /* Second knob without a counterpart in the reference: the adaptive cut.  SMs of one GPU do not stream at
  * the same rate, and CTA c of a grid always runs on the same SM, so with the planner's equal shares the
  * slower SMs finish tens of microseconds after the others.  While this is on (default; environment
@@ -237,8 +222,7 @@ int pd_paged_decode_scaled(int dtype, const pd_params* p, int num_pages, const f
 
 /* What a decode of these params would launch (no counterpart in the reference, which has one kernel shape):
  * out[0] schedule (0 the caller's plan as bound, 1 the same step cut by rows for the head-fused kernel,
- * 2 the caller's plan cut in unequal shares by the adaptive cut, 3 as 1 with work moving between CTAs while
- * the kernel runs, see pd_set_tail_steal), out[1] grid, out[2] tokens per tile,
+ * 2 the caller's plan cut in unequal shares by the adaptive cut), out[1] grid, out[2] tokens per tile,
  * out[3] kv heads per tile, out[4] consumer warps per CTA, out[5] pipeline stages, out[6] CTAs per SM the
  * shape is made for, out[7] needs_merge of that schedule (0 none, 1 merge kernel, 2 merged inside the decode
  * kernel, 3 per row).  Pure host lookup; launches nothing. */

@@ -68,9 +68,6 @@ SIGNATURES = {
     "pd_adaptive_cut_table": (C.c_int, [C.c_int, _vp, _vp, C.c_int]),
     "pd_set_head_fused": (C.c_int, [C.c_int]),
     "pd_head_fused": (C.c_int, []),
-    "pd_set_tail_steal": (C.c_int, [C.c_int]),
-    "pd_tail_steal": (C.c_int, []),
-    "pd_tail_steal_count": (C.c_int, [_vp, C.POINTER(C.c_ulonglong)]),
     "pd_make_plan": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "pd_make_plan_tiled": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "pd_make_plan_weighted": (C.c_int, [C.c_int, _i32p, C.c_int, C.c_int, C.c_int, _vp, C.c_int, C.POINTER(_vp)]),

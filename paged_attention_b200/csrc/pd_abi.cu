@@ -8,7 +8,6 @@
 
 #include "append_kernel.cuh"
 #include "decode_kernel.cuh"
-#include "decode_steal_kernel.cuh"
 #include "plan_kernel.cuh"
 #include "probe_kernel.cuh"
 
@@ -76,11 +75,6 @@ struct KernelInfo {
     void (*launch)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, int, int, unsigned*, const pdk::GatherOut&,
                    const pdk::HeadScales&, const pdk::CtaStats&, cudaStream_t);
     void (*merge)(const pd_params&, int, cudaStream_t);
-    // head-fused shapes only: the same kernel with work moved between CTAs while it runs
-    const void* steal_fn = nullptr;
-    int steal_smem = 0;
-    void (*launch_steal)(const pd_params&, const CUtensorMap&, const CUtensorMap&, int, unsigned*, const pdk::GatherOut&,
-                         const pdk::HeadScales&, const pdk::CtaStats&, const pdk::StealArgs&, cudaStream_t) = nullptr;
 };
 
 template<typename KV, int GROUP, typename C>
@@ -89,14 +83,6 @@ void launch_decode(const pd_params& p, const CUtensorMap& km, const CUtensorMap&
                    cudaStream_t stream) {
     using S = pdk::Shape<KV, GROUP, C>;
     pdk::paged_decode_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, S::SMEM_BYTES, stream>>>(p, km, vm, btl, row_gather, seg_limit, status, gather, scales, stats);
-}
-template<typename KV, int GROUP, typename C>
-void launch_decode_steal(const pd_params& p, const CUtensorMap& km, const CUtensorMap& vm, int btl, unsigned* status,
-                         const pdk::GatherOut& gather, const pdk::HeadScales& scales, const pdk::CtaStats& stats,
-                         const pdk::StealArgs& steal, cudaStream_t stream) {
-    using S = pdk::Shape<KV, GROUP, C>;
-    using SS = pdk::StealShape<KV, GROUP, C>;
-    pdk::paged_decode_steal_kernel<KV, GROUP, C><<<p.num_ctas, S::THREADS, SS::SMEM_BYTES, stream>>>(p, km, vm, btl, status, gather, scales, stats, steal);
 }
 // The merge kernel is launched as a programmatic dependent of the decode kernel before it: its CTAs are
 // placed while the decode grid drains and wait inside the kernel (griddepcontrol.wait) until that grid is
@@ -164,12 +150,8 @@ template<typename KV, int GROUP>
 KernelInfo make_fused_info() {
     using C = typename FusedConfig<KV>::type;
     using S = pdk::Shape<KV, GROUP, C>;
-    KernelInfo k{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
-                 S::SMEM_BYTES, C::MIN_CTAS, C::STAGES, &launch_decode<KV, GROUP, C>, &launch_merge_rows<GROUP>};
-    k.steal_fn = reinterpret_cast<const void*>(&pdk::paged_decode_steal_kernel<KV, GROUP, C>);
-    k.steal_smem = pdk::StealShape<KV, GROUP, C>::SMEM_BYTES;
-    k.launch_steal = &launch_decode_steal<KV, GROUP, C>;
-    return k;
+    return KernelInfo{reinterpret_cast<const void*>(&pdk::paged_decode_kernel<KV, GROUP, C>), S::TILE, S::THREADS,
+                      S::SMEM_BYTES, C::MIN_CTAS, C::STAGES, &launch_decode<KV, GROUP, C>, &launch_merge_rows<GROUP>};
 }
 
 template<typename KV>
@@ -192,9 +174,6 @@ const KernelInfo* fused_info(int dtype, int group) {
 }
 constexpr int FUSED_HEADS = 8;
 int g_head_fused = std::getenv("PD_B200_NO_HEAD_FUSED") == nullptr ? 1 : 0;   // 0 never, 1 where it wins, 2 always
-// Head-fused launches move work between CTAs while they run (decode_steal_kernel.cuh): 0 off, 1 on, 2 on with
-// the row cut skewed on purpose (shares alternate 0.6 / 1.4) so that every launch has work to move: for tests.
-int g_tail_steal = std::getenv("PD_B200_NO_TAIL_STEAL") == nullptr ? 1 : 0;
 
 }  // namespace
 #include "adaptive_cut.hpp"
@@ -220,7 +199,6 @@ int configure(const KernelInfo* k) {
     std::lock_guard<std::mutex> lock(g_cfg_mutex);
     for (auto& c : g_configured) if (c.first == k->fn && c.second == dev) return PD_OK;
     PD_CUDA(cudaFuncSetAttribute(k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->smem));
-    if (k->steal_fn) PD_CUDA(cudaFuncSetAttribute(k->steal_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->steal_smem));
     g_configured.emplace_back(k->fn, dev);
     return PD_OK;
 }
@@ -236,9 +214,8 @@ int status_word(unsigned** out) {
     if (dev < 0 || dev >= MAX_DEVICES) return set_error(PD_INTERNAL, "device index %d out of range", dev);
     std::lock_guard<std::mutex> lock(g_status_mutex);
     if (!g_status[dev]) {
-        // word 0: the status word; bytes 8..15: pieces of work moved between CTAs since the process started
-        PD_CUDA(cudaMalloc(&g_status[dev], 16));
-        PD_CUDA(cudaMemset(g_status[dev], 0, 16));
+        PD_CUDA(cudaMalloc(&g_status[dev], sizeof(unsigned)));
+        PD_CUDA(cudaMemset(g_status[dev], 0, sizeof(unsigned)));
     }
     *out = g_status[dev];
     return PD_OK;
@@ -350,7 +327,6 @@ struct pd_device_plan {
         const int* row_seg_begin = nullptr;
         float* partial_out = nullptr;
         unsigned long long* stats = nullptr;   // per-CTA record of the launches of this schedule (adaptive cut)
-        pdk::StealArgs steal{};                // head-fused rows only: workspace for work moved between CTAs (or null)
     } fused,
       weighted;                    // the caller's (row, kv head) schedule cut in unequal shares (adaptive cut)
     unsigned long long* stats = nullptr;       // record of launches that run the caller's plan as it is
@@ -411,22 +387,6 @@ int pd_set_head_fused(int mode) {
     return PD_OK;
 }
 int pd_head_fused(void) { return g_head_fused; }
-
-int pd_set_tail_steal(int mode) {
-    if (mode < 0 || mode > 2) return set_error(PD_INVALID_ARGUMENT, "set_tail_steal: mode must be 0, 1 or 2");
-    g_tail_steal = mode;
-    return PD_OK;
-}
-int pd_tail_steal(void) { return g_tail_steal; }
-
-int pd_tail_steal_count(void* stream, unsigned long long* out) {
-    if (!out) return set_error(PD_INVALID_ARGUMENT, "tail_steal_count: null argument");
-    unsigned* status = nullptr;
-    if (int rc = status_word(&status)) return rc;
-    PD_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-    PD_CUDA(cudaMemcpy(out, status + 2, sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-    return PD_OK;
-}
 
 int pd_set_adaptive_cut(int on) {
     g_adaptive = on != 0;
@@ -712,15 +672,6 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
             }
         }
     }
-    if (fused_runs && g_tail_steal == 2) {
-        std::vector<float> skew(static_cast<size_t>(rows_plan->num_ctas));
-        for (size_t c = 0; c < skew.size(); c++) skew[c] = c % 2 ? 1.4f : 0.6f;
-        pd_plan* w = nullptr;
-        if (build_plan_weighted(fk->tile, plan->seq_lens.data(), plan->batch, 1, skew, &w) == PD_OK) {
-            delete rows_plan;
-            rows_plan = w;
-        }
-    }
     struct PlanGuard { pd_plan*& p; ~PlanGuard() { delete p; } } guard{rows_plan}, guard_w{weighted_plan};
 
     const size_t seg_bytes  = round16(sizeof(int) * plan->segments.size());
@@ -777,20 +728,7 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
     auto round4 = [](size_t floats) { return (floats + 3) & ~static_cast<size_t>(3); };
     const size_t std_need = round4(rows * (head_dim + 1) + plan->num_items);
     const size_t frows = rows_plan ? (rows_plan->segments.size() / 4) * static_cast<size_t>(group) * FUSED_HEADS : 0;
-    // Behind the head-fused region, when work may move between its CTAs: one word per CTA (zero between launches,
-    // like the counters, and cleared with them), per segment the count and the slots of the pieces taken from it,
-    // and STEALS_PER_CTA partial rows per CTA.
-    const size_t fsegs = rows_plan ? rows_plan->segments.size() / 4 : 0;
-    const size_t fgrid = rows_plan ? static_cast<size_t>(rows_plan->num_ctas) : 0;
-    const size_t fheads = static_cast<size_t>(group) * FUSED_HEADS;
-    const bool steal_ws = rows_plan && g_tail_steal != 0 && head_dim == pdk::HEAD_DIM;
-    const size_t f_words = (frows * (head_dim + 1) + plan->num_items + 1) & ~static_cast<size_t>(1);   // floats; 8-byte aligned
-    const size_t f_nsteal = f_words + 2 * fgrid;
-    const size_t f_slots = f_nsteal + fsegs;
-    const size_t f_sout = round4(f_slots + fsegs * pdk::STEALS_PER_SEG);
-    const size_t f_slse = f_sout + fgrid * pdk::STEALS_PER_CTA * fheads * head_dim;
-    const size_t f_need = !rows_plan ? 0 : steal_ws ? round4(f_slse + fgrid * pdk::STEALS_PER_CTA * fheads)
-                                                    : round4(frows * (head_dim + 1) + plan->num_items);
+    const size_t f_need = rows_plan ? round4(frows * (head_dim + 1) + plan->num_items) : 0;
     const size_t wrows = weighted_plan ? (weighted_plan->segments.size() / 4) * static_cast<size_t>(group) : 0;
     const size_t w_need = weighted_plan ? round4(wrows * (head_dim + 1) + plan->num_items) : 0;
     const size_t need = std_need + f_need + w_need;
@@ -834,16 +772,8 @@ int pd_device_plan_upload(pd_device_plan* dp, const pd_plan* plan, int group, in
         f.cta_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes);
         f.row_seg_begin = reinterpret_cast<const int*>(a + std_bytes + fseg_bytes + fcta_bytes);
         f.partial_out = dp->partial + std_need;
-        const size_t cleared = steal_ws ? f_nsteal : frows * (head_dim + 1) + plan->num_items;   // counters, then the words
-        dp->tails[1] = {f.partial_out + frows * head_dim, sizeof(float) * (cleared - frows * head_dim)};
-        PD_CUDA(cudaMemsetAsync(f.partial_out + frows * (head_dim + 1), 0, sizeof(float) * (cleared - frows * (head_dim + 1)), stream));
-        if (steal_ws) {
-            f.steal.words      = reinterpret_cast<unsigned long long*>(f.partial_out + f_words);
-            f.steal.seg_nsteal = reinterpret_cast<int*>(f.partial_out + f_nsteal);
-            f.steal.seg_slots  = reinterpret_cast<int*>(f.partial_out + f_slots);
-            f.steal.out        = f.partial_out + f_sout;
-            f.steal.lse        = f.partial_out + f_slse;
-        }
+        dp->tails[1] = {f.partial_out + frows * head_dim, sizeof(float) * (frows + plan->num_items)};
+        PD_CUDA(cudaMemsetAsync(f.partial_out + frows * (head_dim + 1), 0, sizeof(int) * plan->num_items, stream));
     }
     dp->weighted = pd_device_plan::Fused{};
     dp->stats = stats_std;
@@ -1090,10 +1020,9 @@ struct Selection {
     int box_heads;                 // kv heads per TMA box: 1, or 8 for the head-fused kernel
     int schedule;                  // 0 the caller's plan, 1 head-fused rows, 2 the caller's plan in unequal shares
     unsigned long long* stats;
-    pdk::StealArgs steal;          // words != null: the head-fused launch moves work between its CTAs
 };
 Selection select_schedule(int dtype, const pd_params* p, const KernelInfo* k, bool gathered, pd_params* scratch) {
-    Selection sel{p, k, 1, 0, nullptr, pdk::StealArgs{}};
+    Selection sel{p, k, 1, 0, nullptr};
     AltSchedules alt;
     {
         std::lock_guard<std::mutex> lock(g_fused_mutex);
@@ -1124,14 +1053,7 @@ Selection select_schedule(int dtype, const pd_params* p, const KernelInfo* k, bo
         scratch->partial_lse = f.partial_out + f.rows * p->head_dim;
         sel.params = scratch;
         sel.schedule = use_fused ? 1 : 2;
-        if (use_fused) {
-            sel.kernel = fk;
-            sel.box_heads = FUSED_HEADS;
-            // rows merged by the separate kernel would not see the pieces that moved
-            if (g_tail_steal && fk->launch_steal && f.steal.words &&
-                (scratch->needs_merge == 0 || scratch->needs_merge == pdk::MERGE_IN_KERNEL))
-                sel.steal = f.steal;
-        }
+        if (use_fused) { sel.kernel = fk; sel.box_heads = FUSED_HEADS; }
         if (g_adaptive) sel.stats = f.stats;
     }
     return sel;
@@ -1176,12 +1098,7 @@ int decode_impl(int dtype, const pd_params* p, int num_pages, const pdk::GatherO
     if (int rc = make_tensor_map(&v_map, dtype, p->v_cache, num_pages, p->num_kv_heads, p->page_size, btl, box_heads, row_gather)) return rc;
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (sel.steal.words) {
-        sel.steal.count = reinterpret_cast<unsigned long long*>(status + 2);
-        k->launch_steal(*p, k_map, v_map, btl, status, gather, scales, pdk::CtaStats{stats_slots}, sel.steal, stream);
-    } else {
-        k->launch(*p, k_map, v_map, btl, row_gather ? 1 : 0, 0, status, gather, scales, pdk::CtaStats{stats_slots}, stream);
-    }
+    k->launch(*p, k_map, v_map, btl, row_gather ? 1 : 0, 0, status, gather, scales, pdk::CtaStats{stats_slots}, stream);
     PD_CUDA(cudaGetLastError());
     if (p->needs_merge && p->needs_merge != pdk::MERGE_IN_KERNEL) {
         k->merge(*p, 0, stream);
@@ -1214,7 +1131,7 @@ int pd_describe_launch(int dtype, const pd_params* p, int* out) {
     if (int rc = find_kernel(dtype, p->head_dim, p->num_q_heads / p->num_kv_heads, &k)) return rc;
     pd_params scratch;
     const Selection sel = select_schedule(dtype, p, k, false, &scratch);
-    out[0] = sel.steal.words ? 3 : sel.schedule;
+    out[0] = sel.schedule;
     out[1] = sel.params->num_ctas;
     out[2] = sel.kernel->tile;
     out[3] = sel.box_heads;

@@ -71,24 +71,6 @@ def head_fused():
     return int(_lib.lib().pd_head_fused())
 
 
-def set_tail_steal(mode):
-    """Head-fused launches move work between CTAs while they run (not in the reference): 0 / False off,
-    1 / True on (the default), 2 on with a deliberately skewed row cut so that every launch moves work."""
-    check(_lib.lib().pd_set_tail_steal(int(mode)))
-
-
-def tail_steal():
-    """The current mode: 0, 1 or 2."""
-    return int(_lib.lib().pd_tail_steal())
-
-
-def tail_steal_count(stream=0):
-    """Pieces of work moved between CTAs on the current device since the process started."""
-    n = C.c_ulonglong(0)
-    check(_lib.lib().pd_tail_steal_count(stream, C.byref(n)))
-    return int(n.value)
-
-
 def set_adaptive_cut(on):
     """Adaptive cut (not in the reference): device plans are cut in shares proportional to the streaming
     rate each CTA showed in earlier launches.  On by default."""
@@ -280,8 +262,7 @@ def paged_decode_static(dtype, params, plan, stream=0, num_pages=0, d_status=Non
     check(_lib.lib().pd_paged_decode_static(int(dtype), C.byref(params), num_segments, num_pages, _ptr(d_status), stream))
 
 
-LAUNCH_SCHEDULES = ("caller's plan", "head-fused rows", "caller's plan in adaptive shares",
-                    "head-fused rows, work moving between CTAs")
+LAUNCH_SCHEDULES = ("caller's plan", "head-fused rows", "caller's plan in adaptive shares")
 
 
 def describe_launch(dtype, params):
@@ -467,5 +448,5 @@ class PagedKVCache:
 
 __all__ = ["KVDtype", "DecodeParams", "DecodePlan", "DevicePlan", "PagedKVCache", "InvalidArgument", "LengthError",
            "kv_dtype_bytes", "kv_dtype_name", "tile_tokens", "wave_ctas", "default_ctas", "make_plan",
-           "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "describe_launch", "set_head_fused", "head_fused", "set_tail_steal", "tail_steal", "tail_steal_count",
+           "make_plan_tiled", "make_plan_weighted", "plan_from_arrays", "paged_decode", "paged_decode_static", "append_tokens", "stream_read", "kernel_status", "describe_launch", "set_head_fused", "head_fused",
            "set_adaptive_cut", "adaptive_cut", "adaptive_cut_reset", "adaptive_cut_refresh", "adaptive_cut_tables"]

@@ -33,15 +33,13 @@ def pa():
 @pytest.fixture(autouse=True)
 def fixed_cut(request):
     """Most tests compare outputs bit for bit between entry points or between steps, so they run with the
-    adaptive cut (shares that follow measured per-CTA rates) and the moving of work between running CTAs
-    switched off; tests of those two switch them on."""
+    adaptive cut (shares that follow measured per-CTA rates) switched off; tests of the adaptive cut itself
+    switch it on."""
     if "pa" not in request.fixturenames:
         yield
         return
     pa = request.getfixturevalue("pa")
-    before, steal = pa.adaptive_cut(), pa.tail_steal()
+    before = pa.adaptive_cut()
     pa.set_adaptive_cut(False)
-    pa.set_tail_steal(0)
     yield
     pa.set_adaptive_cut(before)
-    pa.set_tail_steal(steal)

@@ -1,6 +1,5 @@
 """The configuration that ships: adaptive cut ON (device plans cut in shares that follow the per-CTA rates
-of earlier launches) and work moving between the CTAs of a head-fused launch ON, on top of the default schedule
-choice, at the real sizes of the benchmark workloads.
+of earlier launches) on top of the default schedule choice, at the real sizes of the benchmark workloads.
 
 The other suites switch the adaptive cut off because they compare bits between entry points; here it stays
 on, a dozen plan + run steps let the shares move first, and the outputs are compared with the ORACLE (the
@@ -30,12 +29,10 @@ FP16, FP8 = 0, 1
 
 @pytest.fixture
 def adaptive_on(pa):
-    """Runs after the autouse fixture that switches the adaptive cut and the moving of work between CTAs off."""
+    """Runs after the autouse fixture that switches the adaptive cut off."""
     pa.adaptive_cut_reset()
     pa.set_adaptive_cut(True)
-    pa.set_tail_steal(1)
     yield
-    pa.set_tail_steal(0)
     pa.set_adaptive_cut(False)
     pa.adaptive_cut_reset()
 
@@ -112,7 +109,7 @@ def test_c2_headline_with_moving_shares(torch_cuda, pa, adaptive_on):
     moved = [w for w, n in pa.adaptive_cut_tables() if n > 0 and float(np.abs(w - 1).max()) > 0]
     assert moved, "a 300 us layer gives usable per-CTA rates: the shares have left the equal cut"
     info = cache.describe_launch()
-    assert info["schedule"].startswith("head-fused rows") and info["kv_heads_per_tile"] == 8 and info["tile_tokens"] == 16
+    assert info["schedule"] == "head-fused rows" and info["kv_heads_per_tile"] == 8 and info["tile_tokens"] == 16
     _check(torch, out, _oracle_rows(torch, cache, cfg, FP16, dq, (0, 29, 63), [L] * B, hq, scale))
     # the same step through indirect slots (rows read the slots in reverse) and a plan cut on the device
     slots = list(range(B))[::-1]
