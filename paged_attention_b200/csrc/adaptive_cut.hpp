@@ -21,6 +21,7 @@ struct RateTable {
     bool copy_queued = false;
     std::vector<float> weights;              // mean 1; empty until the first usable record
     int updates = 0;
+    bool resync = false;                     // after a reset: the next copy only re-bases `seen` (launches from before the reset say nothing new)
     // For the device-side planner: shares[0] = 1.0 once weights exist (0.0: cut in equal shares), then
     // shares[1 + c] = (w_0 + .. + w_c-1) / sum(w) for c = 0..grid.  Device memory with a stable address, so a
     // captured plan kernel picks up whatever the host wrote last.
@@ -120,6 +121,7 @@ void fold_readings(RateTable* t, cudaStream_t stream) {
     }
     if (launches == 0) return;                             // nothing ran since the last reading
     t->seen.assign(t->host, t->host + 2 * static_cast<size_t>(n) + 1);
+    if (t->resync) { t->resync = false; return; }
     // Only launches in which every CTA worked, and for long enough (120 us on average) that its few
     // microseconds of ramp-up and epilogue do not matter, say something about streaming rates.
     // (The equal cut can leave the last CTA or two of a grid without work; they keep their weight.)

@@ -431,6 +431,7 @@ int pd_adaptive_cut_reset(void) {
         if (kv.second.shares) cudaMemset(kv.second.shares, 0, sizeof(double));   // device plans go back to equal shares
         if (kv.second.copy_queued) cudaEventSynchronize(kv.second.copied);
         kv.second.copy_queued = false;
+        kv.second.resync = true;   // launches issued since the last copy are not in `host` yet: the next copy only re-bases
         if (kv.second.host) kv.second.seen.assign(kv.second.host, kv.second.host + 2 * static_cast<size_t>(kv.second.grid) + 1);
     }
     return PD_OK;
