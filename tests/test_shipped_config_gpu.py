@@ -226,3 +226,34 @@ def test_unequal_shares_of_random_shapes(index, spec, torch_cuda, pa):
                            v_scale=case.scale)
     assert float(np.abs(out.float().cpu().numpy() - want).max()) <= TOL
     cache.close()
+
+
+@pytest.mark.parametrize("dtype", [FP16, FP8])
+def test_many_launches_leave_nothing_behind(dtype, torch_cuda, pa, adaptive_on):
+    """600 launches of a ragged batch whose rows are cut in up to four pieces, a new plan every seventh launch,
+    outputs pre-filled with NaN: a row that was not merged, or merged before all its pieces had landed, shows."""
+    torch = torch_cuda
+    rng = np.random.default_rng(77)
+    lens = rng.integers(300, 5000, 96).tolist()
+    hq, hkv = 32, 8
+    cache, cfg, scale = _fill(torch, pa, dtype, lens, hkv, 16, 4)
+    B = len(lens)
+    dq = torch.randn(B, hq, 128, device="cuda", dtype=torch.float16, generator=torch.Generator(device="cuda").manual_seed(6))
+    out = torch.zeros_like(dq)
+    slots = list(range(B))
+    first = None
+    for i in range(600):
+        if i % 7 == 0:
+            cache.plan(slots, hq)
+        out.fill_(float("nan"))
+        cache.run(dq, out)
+        if i % 40 == 39:
+            torch.cuda.synchronize()
+            assert torch.isfinite(out).all()
+            if first is None:
+                first = out.clone()
+            assert float((out.float() - first.float()).abs().max()) <= 2.5e-4
+    torch.cuda.synchronize()
+    assert pa.kernel_status() == 0
+    _check(torch, out, _oracle_rows(torch, cache, cfg, dtype, dq, (0, 50, B - 1), lens, hq, scale))
+    cache.close()
